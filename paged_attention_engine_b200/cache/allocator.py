@@ -40,12 +40,13 @@ class AllocResult:
 
 
 class _Table:
-    __slots__ = ("blocks", "tokens", "released")
+    __slots__ = ("blocks", "tokens", "released", "kept")
 
     def __init__(self) -> None:
         self.blocks: list[int] = []   # logical block index -> physical id, HOLE once released
         self.tokens = 0               # tokens reserved so far
-        self.released = 0             # leading logical blocks already given back
+        self.released = 0             # logical blocks below this index were given back, except the first `kept`
+        self.kept = 0                 # leading logical blocks that releases pass over
 
 
 class BlockAllocator:
@@ -69,7 +70,7 @@ class BlockAllocator:
 
     @property
     def num_allocated(self) -> int:
-        return sum(len(t.blocks) - t.released for t in self._tables.values())
+        return sum(len(t.blocks) - max(0, t.released - t.kept) for t in self._tables.values())
 
     def free_block_ids(self) -> tuple[int, ...]:
         """The free list in the order in which blocks will be handed out."""
@@ -106,7 +107,7 @@ class BlockAllocator:
 
     def num_held(self, seq_id) -> int:
         t = self._tables[seq_id]
-        return len(t.blocks) - t.released
+        return len(t.blocks) - max(0, t.released - t.kept)
 
     def blocks_to_append(self, seq_id, count: int) -> int:
         """New blocks that `append_tokens(seq_id, count)` would take (seq_id None: a new request)."""
@@ -131,12 +132,17 @@ class BlockAllocator:
         t.tokens += count
         return AllocResult(AllocStatus.OK, taken)
 
-    def release_before(self, seq_id, position: int) -> tuple[int, ...]:
-        """Gives back the blocks whose tokens all lie before `position`."""
+    def release_before(self, seq_id, position: int, keep_blocks: int = 0) -> tuple[int, ...]:
+        """Gives back the blocks whose tokens all lie before `position`, except the first
+        `keep_blocks` of the table (the same number at every call for one sequence)."""
         t = self._tables[seq_id]
         upto = min(max(position, 0) // self.block_size, len(t.blocks))
+        if t.released == 0:
+            t.kept = keep_blocks
+        elif keep_blocks != t.kept:
+            raise ValueError(f"sequence {seq_id!r}: {t.kept} leading blocks were kept before, {keep_blocks} now")
         freed = []
-        for i in range(t.released, upto):
+        for i in range(max(t.released, t.kept), upto):
             freed.append(t.blocks[i])
             t.blocks[i] = HOLE
         if upto > t.released:

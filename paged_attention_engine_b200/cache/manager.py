@@ -34,6 +34,12 @@ class KVGroupSpec:
     head_dim: int
     window: int                    # 0: every key is kept
     entries: tuple[int, ...]       # schedule positions that own keys and values here
+    value_dim: int = 0             # 0: values have the keys' head size
+    keep_first: int = 0            # with a window: the first keys stay visible, their pages are never given back
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -46,7 +52,8 @@ class CachePlan:
     def bytes_per_block(self, block_size: int, element_size: int) -> int:
         """Bytes of one page id: its keys and values in every entry of every group (each group
         has a pool of its own with the same number of pages)."""
-        return sum(2 * len(g.entries) * g.num_kv_heads * g.head_dim * block_size * element_size for g in self.groups)
+        return sum(len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * block_size * element_size
+                   for g in self.groups)
 
 
 def layer_needs(layer) -> tuple[CacheNeed | None, StateNeed | None]:
@@ -85,7 +92,7 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
         if entry.cache_from is None and need is not None:
             by_need.setdefault(need, []).append(pos)
     groups = tuple(
-        KVGroupSpec(need.num_kv_heads, need.head_dim, need.window, tuple(entries))
+        KVGroupSpec(need.num_kv_heads, need.head_dim, need.window, tuple(entries), need.value_dim, need.keep_first)
         for need, entries in by_need.items()
     )
     entry_group: dict[int, tuple[int, int]] = {}
@@ -97,7 +104,8 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
     for pos, entry in enumerate(spec.schedule):
         if entry.cache_from is not None and needs[pos] is not None:
             src = needs[entry.cache_from]
-            if src is None or (src.num_kv_heads, src.head_dim) != (needs[pos].num_kv_heads, needs[pos].head_dim):
+            if src is None or (src.num_kv_heads, src.head_dim, src.value_dim) != (
+                    needs[pos].num_kv_heads, needs[pos].head_dim, needs[pos].value_dim):
                 raise ValueError(
                     f"schedule[{pos}] reads the cache of entry {entry.cache_from}, whose keys have another shape"
                 )
@@ -276,10 +284,11 @@ class CacheManager:
         for g, (group, a) in enumerate(zip(self.groups, self.allocators)):
             if group.window > 0:
                 first_needed = live.computed - group.window + 1
-                freed = a.release_before(key, first_needed)
+                kept = self.blocks_needed(group.keep_first)      # pages that hold the kept first keys stay
+                freed = a.release_before(key, first_needed, kept)
                 if freed:
                     upto = max(first_needed, 0) // self.block_size
-                    self._tables[g][live.slot, :upto] = HOLE
+                    self._tables[g][live.slot, kept:upto] = HOLE
 
     def free_request(self, key: Hashable) -> int:
         """Gives back every page and the state slot; returns how many pages of the first group."""

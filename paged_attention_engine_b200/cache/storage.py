@@ -22,10 +22,21 @@ class PagedKVCache:
         self.dtype = dtype
         self.device = torch.device(device)
         self.page_size = manager.block_size
+        # A group whose values have the keys' head size is one tensor (keys at index 0, values at 1);
+        # with another value size the values are a tensor of their own and `pools[g]` holds the keys.
         self.pools: list[torch.Tensor] = []
+        self.value_pools: list[torch.Tensor | None] = []
         for group, allocator in zip(plan.groups, manager.allocators):
-            shape = (len(group.entries), 2, allocator.num_blocks, group.num_kv_heads, self.page_size, group.head_dim)
-            self.pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            n, pages = len(group.entries), allocator.num_blocks
+            if group.value_head_dim == group.head_dim:
+                shape = (n, 2, pages, group.num_kv_heads, self.page_size, group.head_dim)
+                self.pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                self.value_pools.append(None)
+            else:
+                self.pools.append(torch.zeros((n, 1, pages, group.num_kv_heads, self.page_size, group.head_dim),
+                                              dtype=dtype, device=self.device))
+                self.value_pools.append(torch.zeros((n, pages, group.num_kv_heads, self.page_size, group.value_head_dim),
+                                                    dtype=dtype, device=self.device))
         self.states: dict[int, torch.Tensor] = {
             # one spare slot behind the real ones, for the padding rows of a captured step
             pos: torch.zeros((manager.slots.num_slots + 1, *need.shape), dtype=need.dtype, device=self.device)
@@ -39,7 +50,7 @@ class PagedKVCache:
             g, i = self.plan.entry_group[position]
             view.group = g
             view.keys = self.pools[g][i, 0]
-            view.values = self.pools[g][i, 1]
+            view.values = self.pools[g][i, 1] if self.value_pools[g] is None else self.value_pools[g][i]
             view.writes = self.plan.entry_writes[position]
         return view
 
@@ -49,11 +60,11 @@ class PagedKVCache:
             tensor[slot].zero_()
 
     def storage_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.pools) + sum(
+        return sum(t.numel() * t.element_size() for t in self.pools + [v for v in self.value_pools if v is not None]) + sum(
             t.numel() * t.element_size() for t in self.states.values()
         )
 
     def bytes_per_token(self) -> int:
         """Key and value bytes that one token adds over all entries of all groups."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.num_kv_heads * g.head_dim * size for g in self.plan.groups)
+        return sum(len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * size for g in self.plan.groups)

@@ -16,6 +16,7 @@ from typing import Any, Callable, Mapping
 
 from .errors import ConfigError
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .bidonex import BidonexConfig
 from .qwen2 import Qwen2Config
 
 
@@ -35,9 +36,11 @@ def register_architecture(name: str, config_class, build_spec) -> None:
 
 def resolve(raw: Mapping[str, Any]):
     """(typed configuration, ModelSpec) for the dictionary of a config.json."""
-    names = raw.get("architectures")
+    # `architectures` is a list whose first name counts; a configuration may also name its one
+    # architecture under `architecture`.
+    names = raw.get("architectures") or ([raw["architecture"]] if raw.get("architecture") else None)
     if not names:
-        raise ConfigError("config.json: key 'architectures' is missing; known: " + ", ".join(sorted(ARCHITECTURES)))
+        raise ConfigError("config.json: key 'architectures' (or 'architecture') is missing; known: " + ", ".join(sorted(ARCHITECTURES)))
     arch = ARCHITECTURES.get(str(names[0]))
     if arch is None:
         raise ConfigError(
@@ -114,3 +117,72 @@ def qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_spec)
+
+
+# --------------------------------------------------------------------------- #
+# Bidonex: token + learned position embedding into a float32 residual stream; per layer ONE
+# LayerNorm whose output both branches read, x <- x + mixer(h) + ff(h); the mixer is a scored
+# sliding-window attention (short convolutions on q, k, v; unit-RMS q and k; temperature, cap,
+# log-distance bias, kept first keys, sink) or the generalized delta rule; the feed-forward is
+# two matrices around the exact GELU, or absent; LayerNorm and an untied head at the end.
+# --------------------------------------------------------------------------- #
+
+# Fixed by the design: the decay is exp(-exp(-1/2) * sigmoid(.)), the unit key's epsilon 1e-6.
+BIDONEX_DECAY_SCALE = 0.6065306597126334
+BIDONEX_KEY_EPS = 1e-6
+
+
+def bidonex_spec(cfg: BidonexConfig) -> ModelSpec:
+    layers = []
+    for i, layer in enumerate(cfg.layers):
+        prefix = f"l{i}"
+        m = layer.mixer
+        if layer.type == "attention":
+            mixer = PartSpec(
+                "scored_window_attention",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
+                    "value_dim": m.vdim, "scale": m.scale, "softcap": m.softcap, "conv_taps": m.conv,
+                    "window": m.window, "keep_first": m.keep_first, "qk_norm_eps": cfg.norm_eps,
+                    "head_temperature": True, "distance_bias": True, "sink": True,
+                },
+                f"{prefix}.mix",
+            )
+        else:
+            mixer = PartSpec(
+                "general_delta",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "head_dim": m.dim, "decay_rank": m.rank,
+                    "decay_scale": BIDONEX_DECAY_SCALE, "key_eps": BIDONEX_KEY_EPS, "norm_eps": cfg.norm_eps,
+                },
+                f"{prefix}.mix",
+            )
+        parts = dict(
+            norm=PartSpec("layer_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine"},
+                          names={"weight": f"{prefix}.norm1", "bias": f"{prefix}.norm1.b"}),
+            mixer=mixer,
+        )
+        if layer.ff:
+            parts["feed_forward"] = PartSpec(
+                "dense_mlp", {"hidden_size": cfg.width, "intermediate_size": layer.ff, "activation": "gelu_erf"},
+                names={"up.weight": f"{prefix}.mlp.up", "down.weight": f"{prefix}.mlp.down"})
+        layers.append(LayerSpec("parallel_residual" if layer.ff else "mixer_residual", parts))
+    return ModelSpec(
+        architecture=cfg.architecture,
+        vocab_size=cfg.vocab,
+        hidden_size=cfg.width,
+        max_positions=cfg.max_positions,
+        embedding=PartSpec(
+            "token_position_embedding",
+            {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "max_positions": cfg.max_positions, "position_scale": 1.0},
+            names={"weight": "embed", "positions": "pos"}),
+        layers=tuple(layers),
+        schedule=tuple(ScheduleEntry(i) for i in range(len(cfg.layers))),
+        final_norm=PartSpec("layer_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine"},
+                            names={"weight": "final.norm", "bias": "final.norm.b"}),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied_to": None},
+                      names={"weight": "head"}),
+    )
+
+
+register_architecture("Bidonex", BidonexConfig, bidonex_spec)

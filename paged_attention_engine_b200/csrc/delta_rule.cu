@@ -1,0 +1,258 @@
+// The generalized delta rule: a recurrent mixer whose per-head state S [key channel, value
+// channel] is carried from token to token in float32.
+//
+//   w_t = exp(-c * sigmoid(w~_t + w0))                  decay per key channel (c a constant of the design)
+//   a_t = sigmoid(a~_t + a_bias)                        removal rate per key channel
+//   u_t = k_t / sqrt(sum(k_t^2) + key_eps)              unit key
+//   S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T
+//   o_t = S_t^T r_t
+//
+// Both terms read the old state. A column of S (one value channel) never meets another column:
+// u^T S and S^T r are sums over key channels only. So a block owns some value channels of one head
+// of one request, a thread owns a run of key channels of one value channel in registers, and the
+// two sums are reductions over the few neighbouring lanes that share a value channel. Tokens of a
+// portion are taken in tiles: the tile's vectors (w, a u, u, k, r, v) are prepared by all
+// threads into shared memory, then the recurrence walks the tile without a block-wide barrier.
+// The state is read at the start of a portion and written back at its end, so a prompt cut into
+// portions, or decoded token by token, computes bit for bit what the whole prompt computes.
+//
+// A second kernel finishes the output: each head's o over its root mean square, times a weight,
+// times sigmoid of the gate projection, rounded to the engine's element type.
+//
+// Everything here is float32: the projections come in as float32 rows, the state is float32.
+#include "common.cuh"
+
+using namespace pae;
+
+namespace {
+
+struct DeltaParams {
+  const float* proj;       // [tokens, ld]: r, k, v, a~, gate at their column offsets
+  int ld, r_off, k_off, v_off, a_off;
+  const float* w_pre;      // [tokens, heads * d]: w~
+  const float* w0;         // [heads * d]
+  const float* a_bias;     // [heads * d]
+  float* state;            // [slots, heads, d (value channel), d (key channel)]
+  float* o;                // [tokens, heads * d]
+  const int* q_start;      // [entries + 1]
+  const int* state_slot;   // [entries]
+  int heads, d, columns;   // columns: value channels per block
+  int tile;                // tokens prepared at a time
+  float decay_scale, key_eps;
+};
+
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
+
+// RPT key channels per thread, P threads per value channel (a power of two of at most 32).
+template <int RPT>
+__global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) {
+  dependent_launch_prologue();
+  extern __shared__ float smem[];
+  const int e = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * p.columns;
+  const int d = p.d, dp = P * RPT;
+  const int tid = threadIdx.x, threads = blockDim.x;
+  const int column = tid / P, part = tid % P;
+  const int j = j0 + column;
+  const bool owns = column < p.columns && j < d;
+  const int first = p.q_start[e], count = p.q_start[e + 1] - first;
+
+  // per tile token: u, w, au, k, r [dp each], v [columns]
+  const int per_token = 5 * dp + p.columns;
+  float S[RPT];
+  float* mine = p.state + (((size_t)p.state_slot[e] * p.heads + h) * d + (owns ? j : 0)) * d;
+#pragma unroll
+  for (int rr = 0; rr < RPT; ++rr) {
+    const int i = part * RPT + rr;
+    S[rr] = (owns && i < d) ? mine[i] : 0.f;
+  }
+
+  const int lane = tid & 31, warp = tid >> 5, warps = threads >> 5;
+  for (int t0 = 0; t0 < count; t0 += p.tile) {
+    const int n = min(p.tile, count - t0);
+    __syncthreads();                            // the tile before is no longer read
+    for (int idx = tid; idx < n * dp; idx += threads) {
+      const int tok = idx / dp, i = idx - tok * dp;
+      float* at = smem + (size_t)tok * per_token;
+      float k = 0.f, r = 0.f, w = 0.f, a = 0.f;
+      if (i < d) {
+        const float* row = p.proj + (size_t)(first + t0 + tok) * p.ld;
+        const int c = h * d + i;
+        k = row[p.k_off + c];
+        r = row[p.r_off + c];
+        a = sigmoidf(row[p.a_off + c] + p.a_bias[c]);
+        w = expf(-p.decay_scale * sigmoidf(p.w_pre[(size_t)(first + t0 + tok) * p.heads * d + c] + p.w0[c]));
+      }
+      at[dp + i] = w;
+      at[2 * dp + i] = a;                       // times u below
+      at[3 * dp + i] = k;
+      at[4 * dp + i] = r;
+    }
+    for (int idx = tid; idx < n * p.columns; idx += threads) {
+      const int tok = idx / p.columns, c = idx - tok * p.columns;
+      smem[(size_t)tok * per_token + 5 * dp + c] =
+          (j0 + c < d) ? p.proj[(size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c] : 0.f;
+    }
+    __syncthreads();
+    for (int tok = warp; tok < n; tok += warps) {        // the unit key: a warp per token
+      float* at = smem + (size_t)tok * per_token;
+      float squares = 0.f;
+      for (int i = lane; i < d; i += 32) squares = fmaf(at[3 * dp + i], at[3 * dp + i], squares);
+      const float inv = 1.f / sqrtf(warp_sum(squares) + p.key_eps);
+      for (int i = lane; i < dp; i += 32) {
+        const float u = at[3 * dp + i] * inv;
+        at[i] = u;
+        at[2 * dp + i] *= u;
+      }
+    }
+    __syncthreads();
+    for (int tok = 0; tok < n; ++tok) {
+      const float* at = smem + (size_t)tok * per_token + part * RPT;
+      float us = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) us = fmaf(at[rr], S[rr], us);
+      for (int o = P >> 1; o > 0; o >>= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
+      const float v = owns ? smem[(size_t)tok * per_token + 5 * dp + column] : 0.f;
+      float out = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) {
+        const float s = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us, at[dp + rr] * S[rr]));
+        S[rr] = s;
+        out = fmaf(s, at[4 * dp + rr], out);
+      }
+      for (int o = P >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      if (owns && part == 0) p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = out;
+    }
+  }
+  if (owns) {
+#pragma unroll
+    for (int rr = 0; rr < RPT; ++rr) {
+      const int i = part * RPT + rr;
+      if (i < d) mine[i] = S[rr];
+    }
+  }
+}
+
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * sigmoid(gate[t, h, :]); a warp per (token, head).
+template <typename T>
+__global__ void delta_output_kernel(T* __restrict__ out, const float* __restrict__ o, const float* __restrict__ gate,
+                                    int gate_ld, const float* __restrict__ weight, int tokens, int heads, int d, float eps) {
+  dependent_launch_prologue();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = unit / heads, h = unit - t * heads;
+  const float* row = o + ((size_t)t * heads + h) * d;
+  float squares = 0.f;
+  for (int i = lane; i < d; i += 32) squares = fmaf(row[i], row[i], squares);
+  const float inv = 1.f / sqrtf(warp_sum(squares) / (float)d + eps);
+  for (int i = lane; i < d; i += 32) {
+    float v = row[i] * inv;
+    if (weight != nullptr) v *= weight[h * d + i];
+    if (gate != nullptr) v *= sigmoidf(gate[(size_t)t * gate_ld + h * d + i]);
+    out[((size_t)t * heads + h) * d + i] = from_float<T>(v);
+  }
+}
+
+// out[t, c] = tanh(x[t, offset + c]) for c < width: the activation between the two small matrices
+// of the decay's projection.
+template <typename T>
+__global__ void tanh_columns_kernel(T* __restrict__ out, const float* __restrict__ x, int ld, int offset, int width, long long total) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int c = (int)(i - t * width);
+  out[i] = from_float<T>(tanhf(x[t * ld + offset + c]));
+}
+
+int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p *= 2;
+  return p;
+}
+
+}  // namespace
+
+// How a head of size d is laid out: key channels per thread (0: the size is not taken) and threads
+// per value channel.
+PAE_EXPORT int pae_delta_rule_layout(int d, int* threads_per_column) {
+  if (d < 1 || d > 256) return 0;
+  const int choices[4] = {8, 16, 32, 64};
+  for (int rpt : choices) {
+    const int P = pow2_at_least((d + rpt - 1) / rpt);
+    if (P <= 32 && (d * P + 31) / 32 * 32 <= 1024) {
+      if (threads_per_column != nullptr) *threads_per_column = P;
+      return rpt;
+    }
+  }
+  return 0;
+}
+
+// proj float32 [tokens, ld] holds r, k, v, a~ at the given column offsets (heads * d columns each);
+// w_pre float32 [tokens, heads * d]; state float32 [slots, heads, d, d] (value channel major);
+// o float32 [tokens, heads * d]. `column_splits` blocks share a head's value channels.
+PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, const float* proj, int ld, int r_off, int k_off, int v_off,
+                                   int a_off, const float* w_pre, const float* w0, const float* a_bias,
+                                   const int* q_start, const int* state_slot, int entries, int heads, int d,
+                                   int column_splits, float decay_scale, float key_eps, void* stream) {
+  if (entries == 0) return 0;
+  int P = 0;
+  const int rpt = pae_delta_rule_layout(d, &P);
+  if (rpt == 0) return fail(2, "delta_rule_scan: head size %d is outside [1, 256]", d);
+  if (entries > 2147483647 / 2 || heads > 65535) return fail(3, "delta_rule_scan: %d requests x %d heads exceed one launch", entries, heads);
+  if (column_splits < 1 || column_splits > d) return fail(2, "delta_rule_scan: %d blocks for %d value channels", column_splits, d);
+  DeltaParams p{};
+  p.proj = proj; p.ld = ld; p.r_off = r_off; p.k_off = k_off; p.v_off = v_off; p.a_off = a_off;
+  p.w_pre = w_pre; p.w0 = w0; p.a_bias = a_bias; p.state = state; p.o = o; p.q_start = q_start; p.state_slot = state_slot;
+  p.heads = heads; p.d = d; p.columns = (d + column_splits - 1) / column_splits;
+  p.decay_scale = decay_scale; p.key_eps = key_eps;
+  const int dp = P * rpt;
+  const int per_token = 5 * dp + p.columns;
+  int tile = 16;
+  while (tile > 1 && (size_t)tile * per_token * sizeof(float) > 40 * 1024) tile /= 2;
+  p.tile = tile;
+  const size_t bytes = (size_t)tile * per_token * sizeof(float);
+  const int threads = (p.columns * P + 31) / 32 * 32;
+  dim3 grid(entries, heads, (d + p.columns - 1) / p.columns);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (rpt) {
+    case 8: launch_kernel(delta_scan_kernel<8>, grid, threads, bytes, s, p, P); break;
+    case 16: launch_kernel(delta_scan_kernel<16>, grid, threads, bytes, s, p, P); break;
+    case 32: launch_kernel(delta_scan_kernel<32>, grid, threads, bytes, s, p, P); break;
+    default: launch_kernel(delta_scan_kernel<64>, grid, threads, bytes, s, p, P); break;
+  }
+  return check_launch("delta_rule_scan");
+}
+
+// out [tokens, heads * d] (dtype) from o float32; gate float32 rows of pitch gate_ld (the gate's
+// columns start at `gate`), weight float32 [heads * d]; either may be null.
+PAE_EXPORT int pae_delta_rule_output(void* out, const float* o, const float* gate, int gate_ld, const float* weight,
+                                     int tokens, int heads, int d, float eps, int dtype, void* stream) {
+  if (tokens == 0 || heads == 0) return 0;
+  const long long units = (long long)tokens * heads;
+  const unsigned blocks = (unsigned)((units + 3) / 4);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32)
+    launch_kernel(delta_output_kernel<float>, blocks, 128, 0, s, (float*)out, o, gate, gate_ld, weight, tokens, heads, d, eps);
+  else if (dtype == kBF16)
+    launch_kernel(delta_output_kernel<__nv_bfloat16>, blocks, 128, 0, s, (__nv_bfloat16*)out, o, gate, gate_ld, weight, tokens, heads, d, eps);
+  else
+    return fail(1, "delta_rule_output: unknown dtype %d", dtype);
+  return check_launch("delta_rule_output");
+}
+
+PAE_EXPORT int pae_tanh_columns(void* out, const float* x, int tokens, int ld, int offset, int width, int dtype, void* stream) {
+  const long long total = (long long)tokens * width;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32)
+    launch_kernel(tanh_columns_kernel<float>, blocks, 256, 0, s, (float*)out, x, ld, offset, width, total);
+  else if (dtype == kBF16)
+    launch_kernel(tanh_columns_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, x, ld, offset, width, total);
+  else
+    return fail(1, "tanh_columns: unknown dtype %d", dtype);
+  return check_launch("tanh_columns");
+}
+
+PAE_DEFINE_LAST_ERROR()

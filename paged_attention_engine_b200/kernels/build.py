@@ -45,6 +45,10 @@ FAMILIES: dict[str, list[str]] = {
     "attention_mma": ["attention_mma.cu", "attention_mma.cuh", "common.cuh"],
     "fused_decode": ["fused_decode.cu", "common.cuh"],
     "attention_tcgen05": ["attention_tcgen05.cu", "common.cuh"],
+    "norm_act": ["norm_act.cu", "common.cuh"],
+    "short_conv": ["short_conv.cu", "common.cuh"],
+    "attention_scored": ["attention_scored.cu", "common.cuh"],
+    "delta_rule": ["delta_rule.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

@@ -818,3 +818,206 @@ def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index, kee
                                _ptr(kept[0]), _ptr(kept[1]), _ptr(kept[2]), _ptr(kept[3]),
                                _stream()), 2 if words else 1)
     return out
+
+
+# ----------------------------------------------------------------------------------- #
+# Kernels of decoders with a float32 residual stream, short convolutions, a scored
+# attention rule and recurrent state (csrc/norm_act.cu, short_conv.cu, attention_scored.cu,
+# delta_rule.cu). Each takes the engine's element type where it reads or writes
+# activations and float32 where the arithmetic is float32 by design.
+# ----------------------------------------------------------------------------------- #
+
+def embedding_positions(ids, positions, table, position_table, feedback=None, position_scale: float = 1.0) -> torch.Tensor:
+    """float32 [tokens, width]: table[id] + position_scale * position_table[position]. `feedback`
+    as in `embedding`."""
+    _need(table, "embedding_positions: table")
+    _need(position_table, "embedding_positions: position table", table.dtype)
+    _need(ids, "embedding_positions: ids", torch.int32)
+    _need(positions, "embedding_positions: positions", torch.int32)
+    if position_table.shape[1] != table.shape[1]:
+        raise KernelError(f"embedding_positions: rows of {table.shape[1]} and of {position_table.shape[1]}")
+    last_token, state_slot, seq_index = feedback if feedback is not None else (None, None, None)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_embedding_positions(_ptr(out), _ptr(table), _ptr(position_table), _ptr(ids), _ptr(positions),
+                                            _ptr(last_token), _ptr(state_slot), _ptr(seq_index), ids.numel(),
+                                            table.shape[0], position_table.shape[0], table.shape[1], position_scale,
+                                            _code(table), _stream()))
+    return out
+
+
+def layer_norm(x, weight: torch.Tensor, bias: torch.Tensor | None, eps: float, out_dtype=None) -> torch.Tensor:
+    """(x - mean) / sqrt(var + eps) * weight + bias over the last axis; x float32 or the engine's
+    dtype, the result in `out_dtype` (x's when None)."""
+    x = materialized(x)
+    _need(x, "layer_norm: x")
+    _need(weight, "layer_norm: weight", torch.float32)
+    if bias is not None:
+        _need(bias, "layer_norm: bias", torch.float32)
+    width = x.shape[-1]
+    if weight.numel() != width or (bias is not None and bias.numel() != width):
+        raise KernelError(f"layer_norm: weight of {weight.numel()} for rows of {width}")
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    rows = x.numel() // width if x.numel() else 0
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_layer_norm(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), rows, width, eps, _code(x), _code(out), _stream()))
+    return out
+
+
+GELU_KINDS = {"gelu_erf": 0, "gelu_tanh": 1}
+
+
+def gelu(x, kind: str = "gelu_erf") -> torch.Tensor:
+    x = materialized(x)
+    _need(x, "gelu: x")
+    if kind not in GELU_KINDS:
+        raise KernelError(f"gelu: kind '{kind}' (known: {', '.join(GELU_KINDS)})")
+    out = torch.empty_like(x)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_gelu(_ptr(out), _ptr(x), x.numel(), GELU_KINDS[kind], _code(x), _stream()))
+    return out
+
+
+def conv_heads_cache_write(proj, taps_weight, state, positions, seq_index, q_start, q_pos0, state_slot, slots, keys,
+                           values, num_heads, num_kv_heads, head_dim, value_dim, page_size, normalize: bool, eps: float,
+                           out_dtype) -> torch.Tensor:
+    """The short causal convolution of a float32 q|k|v projection [tokens, channels] (taps_weight
+    float32 [channels, taps] or None; state float32 [slots, taps - 1, channels] holds every
+    request's last projected rows and is brought up to date), unit RMS per q and k head when
+    `normalize`, k and v written to their pages at `slots`. Returns q [tokens, heads * head_dim]
+    in `out_dtype`."""
+    proj = materialized(proj)
+    _need(proj, "conv_heads_cache_write: projection", torch.float32)
+    channels = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
+    tokens = proj.shape[0]
+    if proj.shape[1] != channels:
+        raise KernelError(f"conv_heads_cache_write: rows of {proj.shape[1]} for {channels} channels")
+    taps = 1
+    if taps_weight is not None:
+        _need(taps_weight, "conv_heads_cache_write: taps", torch.float32)
+        if taps_weight.dim() != 2 or taps_weight.shape[0] != channels:
+            raise KernelError(f"conv_heads_cache_write: taps are {tuple(taps_weight.shape)} for {channels} channels")
+        taps = int(taps_weight.shape[1])
+    if taps > 1:
+        _need(state, "conv_heads_cache_write: state", torch.float32)
+        if tuple(state.shape[1:]) != (taps - 1, channels):
+            raise KernelError(f"conv_heads_cache_write: state rows are {tuple(state.shape[1:])}, ({taps - 1}, {channels}) is needed")
+    for name, t in (("positions", positions), ("seq_index", seq_index), ("q_start", q_start), ("q_pos0", q_pos0),
+                    ("state_slot", state_slot)):
+        _need(t, f"conv_heads_cache_write: {name}", torch.int32)
+    if slots is not None:
+        _need(slots, "conv_heads_cache_write: slots", torch.int32)
+        _need(keys, "conv_heads_cache_write: keys", out_dtype)
+        _need(values, "conv_heads_cache_write: values", out_dtype)
+    q = torch.empty((tokens, num_heads * head_dim), dtype=out_dtype, device=proj.device)
+    lib = _lib("short_conv")
+    _set_bounds("short_conv", keys if slots is not None else None)
+    _check(lib, lib.pae_conv_heads_cache_write(
+        _ptr(q), _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), _ptr(proj),
+        _ptr(taps_weight), _ptr(state if taps > 1 else None), _ptr(positions), _ptr(seq_index), _ptr(q_start), _ptr(q_pos0),
+        _ptr(state_slot), _ptr(slots), tokens, taps, num_heads, num_kv_heads, head_dim, value_dim, page_size,
+        1 if normalize else 0, eps, _DTYPE_CODE[out_dtype], _stream()))
+    if taps > 1:
+        _check(lib, lib.pae_conv_state_update(_ptr(state), _ptr(proj), _ptr(q_start), _ptr(q_pos0), _ptr(state_slot),
+                                              state_slot.numel(), taps, channels, _stream()))
+    return q
+
+
+def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
+                           value_dim, page_size, max_q_len, scale, softcap=0.0, temp=None, r1=None, r2=None, sink=None,
+                           window: int = 0, keep_first: int = 0) -> torch.Tensor:
+    """Attention of every token of the step over its request's pages under a score rule:
+    (q . k) * scale * temp[h], capped by softcap * tanh(. / softcap), minus r1[h] * log(1 + r2[h] *
+    distance), a window that keeps the first `keep_first` keys, and a sink logit per head in the
+    softmax's denominator. temp, r1, r2, sink are float32 [heads] or None. -> [tokens, heads * value_dim]."""
+    q = materialized(q)
+    _need(q, "paged_attention_scored: q")
+    _need(keys, "paged_attention_scored: keys", q.dtype)
+    _need(values, "paged_attention_scored: values", q.dtype)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_pos0", q_pos0), ("kv_len", kv_len)):
+        _need(t, f"paged_attention_scored: {name}", torch.int32)
+    for name, t in (("temp", temp), ("r1", r1), ("r2", r2), ("sink", sink)):
+        if t is not None:
+            _need(t, f"paged_attention_scored: {name}", torch.float32)
+            if t.numel() != num_heads:
+                raise KernelError(f"paged_attention_scored: {name} has {t.numel()} numbers for {num_heads} heads")
+    tokens = q.shape[0]
+    if q.shape[1] != num_heads * head_dim:
+        raise KernelError(f"paged_attention_scored: q rows of {q.shape[1]} for {num_heads} heads of {head_dim}")
+    out = torch.empty((tokens, num_heads * value_dim), dtype=q.dtype, device=q.device)
+    lib = _lib("attention_scored")
+    _set_bounds("attention_scored", keys)
+    _check(lib, lib.pae_paged_attention_scored(
+        _ptr(out), _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start), _ptr(q_pos0),
+        _ptr(kv_len), kv_len.numel(), max_q_len, num_heads, num_kv_heads, head_dim, value_dim, page_size, scale,
+        float(softcap or 0.0), _ptr(temp), _ptr(r1), _ptr(r2), _ptr(sink), int(window), int(keep_first), _code(q), _stream()))
+    return out
+
+
+def tanh_columns(x, offset: int, width: int, out_dtype) -> torch.Tensor:
+    """tanh of columns [offset, offset + width) of float32 rows, in `out_dtype`."""
+    x = materialized(x)
+    _need(x, "tanh_columns: x", torch.float32)
+    if offset < 0 or offset + width > x.shape[1]:
+        raise KernelError(f"tanh_columns: columns {offset}..{offset + width} of rows of {x.shape[1]}")
+    out = torch.empty((x.shape[0], width), dtype=out_dtype, device=x.device)
+    lib = _lib("delta_rule")
+    _check(lib, lib.pae_tanh_columns(_ptr(out), _ptr(x), x.shape[0], x.shape[1], offset, width, _DTYPE_CODE[out_dtype], _stream()))
+    return out
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _SM_COUNT[index]
+
+
+def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state, q_start, state_slot, num_seqs, num_heads,
+               head_dim, decay_scale: float, key_eps: float, norm_eps: float, out_dtype) -> torch.Tensor:
+    """The generalized delta rule over the step's tokens, from and into the per-request state
+    (float32 [slots, heads, head_dim, head_dim]): see csrc/delta_rule.cu. `proj` float32 [tokens, ld]
+    holds r, k, v, the removal rate's and the gate's projections at `offsets` = (r, k, v, a) and
+    `gate_offset`; `w_pre` float32 [tokens, heads * head_dim] the decay's. Returns
+    rms_norm_per_head(o) * norm_weight * sigmoid(gate) as [tokens, heads * head_dim] in `out_dtype`."""
+    proj = materialized(proj)
+    w_pre = materialized(w_pre)
+    _need(proj, "delta_rule: projections", torch.float32)
+    _need(w_pre, "delta_rule: decay projection", torch.float32)
+    _need(state, "delta_rule: state", torch.float32)
+    for name, t in (("w0", w0), ("a_bias", a_bias), ("norm weight", norm_weight)):
+        _need(t, f"delta_rule: {name}", torch.float32)
+        if t.numel() != num_heads * head_dim:
+            raise KernelError(f"delta_rule: {name} has {t.numel()} numbers for {num_heads} heads of {head_dim}")
+    _need(q_start, "delta_rule: q_start", torch.int32)
+    _need(state_slot, "delta_rule: state_slot", torch.int32)
+    tokens, ld = proj.shape
+    width = num_heads * head_dim
+    if tuple(w_pre.shape) != (tokens, width):
+        raise KernelError(f"delta_rule: the decay projection is {tuple(w_pre.shape)}, [{tokens}, {width}] is needed")
+    if tuple(state.shape[1:]) != (num_heads, head_dim, head_dim):
+        raise KernelError(f"delta_rule: state rows are {tuple(state.shape[1:])}")
+    for off in (*offsets, gate_offset):
+        if off < 0 or off + width > ld:
+            raise KernelError(f"delta_rule: columns {off}..{off + width} of rows of {ld}")
+    lib = _lib("delta_rule")
+    per_column = c_int(0)
+    if lib.pae_delta_rule_layout(head_dim, ctypes.byref(per_column)) == 0:
+        raise KernelError(f"delta_rule: head size {head_dim} is not supported (1 to 256)")
+    # Few (request, head) pairs leave SMs idle: a head's value channels are shared out over blocks
+    # (the recurrence of a value channel needs no other), at least a warp's worth of threads each.
+    splits, sms = 1, _sm_count(proj.device)
+    while (num_seqs * num_heads * splits < sms and head_dim % (2 * splits) == 0
+           and (head_dim // (2 * splits)) * per_column.value >= 64):
+        splits *= 2
+    o = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
+    _check(lib, lib.pae_delta_rule_scan(_ptr(o), _ptr(state), _ptr(proj), ld, offsets[0], offsets[1], offsets[2], offsets[3],
+                                        _ptr(w_pre), _ptr(w0), _ptr(a_bias), _ptr(q_start), _ptr(state_slot), num_seqs,
+                                        num_heads, head_dim, splits, decay_scale, key_eps, _stream()))
+    out = torch.empty((tokens, width), dtype=out_dtype, device=proj.device)
+    _check(lib, lib.pae_delta_rule_output(_ptr(out), _ptr(o), proj.data_ptr() + 4 * gate_offset, ld, _ptr(norm_weight), tokens,
+                                          num_heads, head_dim, norm_eps, _DTYPE_CODE[out_dtype], _stream()))
+    return out

@@ -56,20 +56,37 @@ class TensorSpec:
     vector   a bias: held in float32; drawn N(0, 0.02).
     scale    a norm's weight: held in float32; drawn 1 + N(0, 0.02).
     index    an integer table: held as int32; drawn uniformly from [0, shape[0]).
+    taps     the weights of a short convolution: held in float32; drawn uniformly from (-1, 1).
+    rate     a small positive constant (the slope inside a logarithm): held in float32;
+             drawn uniformly from (0, 0.1).
+
+    A dimension of -1 in `shape` is whatever the checkpoint has (the part reads the size from
+    its tensor); `random_size` is what the random-weights mode draws there.
     """
 
     name: str
     shape: tuple[int, ...]
     kind: str = "matrix"
+    random_size: int = 16
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(want in (-1, have) for want, have in zip(self.shape, shape))
+
+    def drawn_shape(self) -> tuple[int, ...]:
+        return tuple(self.random_size if n == -1 else n for n in self.shape)
 
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values of a mixer: `window` 0 keeps all of them, w > 0 the last w."""
+    """Keys and values of a mixer: `window` 0 keeps all of them, w > 0 the last w and, before
+    them, the first `keep_first`. `value_dim` 0: values have the keys' head size."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -18,3 +18,29 @@ class PreNormResidual(Block):
         hidden = layer.mixer.forward(ctx, normed, ctx.ops.materialized(hidden), cache)
         normed = layer.feed_forward_norm.forward(ctx, hidden)
         return layer.feed_forward.forward(ctx, normed, ctx.ops.materialized(hidden))
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidual(Block):
+    """One norm whose output both branches read: x <- x + mixer(norm(x)) + ff(norm(x)). Each
+    branch's last product adds what came before it in its epilogue, in the residual's dtype
+    (float32 when the embedding makes a float32 stream)."""
+
+    roles = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    def forward(self, ctx, hidden, layer, cache):
+        hidden = ctx.ops.materialized(hidden)
+        normed = layer.norm.forward(ctx, hidden)
+        hidden = layer.mixer.forward(ctx, normed, hidden, cache)
+        return layer.feed_forward.forward(ctx, normed, ctx.ops.materialized(hidden))
+
+
+@BLOCKS.register("mixer_residual")
+class MixerResidual(Block):
+    """A layer without a feed-forward: x <- x + mixer(norm(x))."""
+
+    roles = {"norm": "norm", "mixer": "mixer"}
+
+    def forward(self, ctx, hidden, layer, cache):
+        hidden = ctx.ops.materialized(hidden)
+        return layer.mixer.forward(ctx, layer.norm.forward(ctx, hidden), hidden, cache)

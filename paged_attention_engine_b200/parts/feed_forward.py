@@ -45,3 +45,30 @@ class SwiGLU(Part):
         else:
             hidden = ops.silu_mul(ops.linear(x, self.gate_up_weight, None))
         return ops.linear(hidden, self.down_weight, None, residual)
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(Part):
+    """down(act(up(x))) without biases. params: hidden_size, intermediate_size, activation
+    ("gelu_erf": 0.5 z (1 + erf(z / sqrt 2)), or "gelu_tanh"). tensors: up.weight, down.weight.
+    The residual may be float32 while x is in the engine's dtype: the down projection adds it in
+    its epilogue and leaves the residual's dtype."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        hidden, inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        return [
+            TensorSpec(spec.tensor_name("up.weight"), (inter, hidden), "matrix"),
+            TensorSpec(spec.tensor_name("down.weight"), (hidden, inter), "matrix"),
+        ]
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.activation = str(spec.params.get("activation", "gelu_erf"))
+        self.up_weight = tensors.pop(spec.tensor_name("up.weight"))
+        self.down_weight = tensors.pop(spec.tensor_name("down.weight"))
+
+    def forward(self, ctx, x, residual):
+        ops = self.ops
+        hidden = ops.gelu(ops.linear(x, self.up_weight, None), self.activation)
+        return ops.linear(hidden, self.down_weight, None, residual, out_dtype=residual.dtype if residual is not None else None)

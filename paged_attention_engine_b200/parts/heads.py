@@ -52,3 +52,29 @@ class LMHead(Part):
 
     def forward(self, ctx, rows):
         return self.ops.linear(rows, self.weight, None, None, out_dtype=torch.float32)
+
+
+@EMBEDDINGS.register("token_position_embedding")
+class TokenPositionEmbedding(Part):
+    """table[token] + position_scale * positions[p] as a float32 residual stream. params:
+    vocab_size, hidden_size, max_positions, position_scale (default 1). tensors: weight
+    [vocab, hidden], positions [max_positions, hidden]."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        hidden = int(spec.params["hidden_size"])
+        return [TensorSpec(spec.tensor_name("weight"), (int(spec.params["vocab_size"]), hidden), "matrix"),
+                TensorSpec(spec.tensor_name("positions"), (int(spec.params["max_positions"]), hidden), "matrix")]
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors[spec.tensor_name("weight")]
+        self.positions = tensors[spec.tensor_name("positions")]
+        self.position_scale = float(spec.params.get("position_scale", 1.0))
+
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        return 2 * num_tokens * self.weight.shape[1] * self.weight.element_size()
+
+    def forward(self, ctx):
+        return self.ops.embedding_positions(ctx.token_ids, ctx.positions, self.weight, self.positions,
+                                            getattr(ctx, "feedback", None), self.position_scale)

@@ -24,3 +24,29 @@ class RMSNorm(Part):
 
     def forward(self, ctx, x):
         return self.ops.rms_norm(x, self.weight, self.eps)
+
+
+@NORMS.register("layer_norm")
+class LayerNorm(Part):
+    """(x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations;
+    statistics in 32-bit. params: size, eps, bias (default True), out ("engine": the result is
+    in the engine's dtype even when x, a float32 residual stream, is not; default: x's dtype).
+    tensors: weight [size], bias [size]."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        size = int(spec.params["size"])
+        out = [TensorSpec(spec.tensor_name("weight"), (size,), "scale")]
+        if spec.params.get("bias", True):
+            out.append(TensorSpec(spec.tensor_name("bias"), (size,), "vector"))
+        return out
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.eps = float(spec.params["eps"])
+        self.weight = tensors[spec.tensor_name("weight")]
+        self.bias = tensors[spec.tensor_name("bias")] if spec.params.get("bias", True) else None
+        self.out_dtype = runtime.dtype if spec.params.get("out") == "engine" else None
+
+    def forward(self, ctx, x):
+        return self.ops.layer_norm(x, self.weight, self.bias, self.eps, self.out_dtype)

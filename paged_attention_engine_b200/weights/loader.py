@@ -11,7 +11,7 @@ Storage on the device:
   matrices     the engine's dtype (bfloat16 or float32); in a bfloat16 engine a matrix
                that the file stores in 32-bit stays in 32-bit and runs on the slower
                kernel that takes such a weight;
-  biases and norm weights   float32 (widening bfloat16 is exact);
+  biases, norm weights, convolution taps and per-head constants   float32 (widening bfloat16 is exact);
   integer tables            int32.
 """
 
@@ -78,7 +78,7 @@ def check_against_specs(
     wrong = [
         f"{n}: file has {tuple(present[n])}, the model reads {tuple(expected[n].shape)}"
         for n in expected
-        if n in present and tuple(present[n]) != tuple(expected[n].shape)
+        if n in present and not expected[n].fits(present[n])
     ]
     if not (missing or unexpected or wrong):
         return
@@ -100,7 +100,7 @@ def place(tensor: torch.Tensor, spec: TensorSpec, dtype: torch.dtype, device) ->
         return tensor.to(device=device, dtype=torch.int32).contiguous()
     if not tensor.dtype.is_floating_point:
         raise WeightsError(f"{spec.name}: stored as {tensor.dtype}, a floating-point tensor is read")
-    if spec.kind in ("vector", "scale"):
+    if spec.kind in ("vector", "scale", "taps", "rate"):
         return tensor.to(device=device, dtype=torch.float32).contiguous()
     if dtype == torch.bfloat16 and tensor.dtype in (torch.float32, torch.float64):
         return tensor.to(device=device, dtype=torch.float32).contiguous()

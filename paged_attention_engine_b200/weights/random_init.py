@@ -2,7 +2,8 @@
 configuration and a seed.
 
 The draw follows the tensor's kind: matrices and biases N(0, 0.02), norm weights
-1 + N(0, 0.02), integer tables uniform. Tensors are drawn in the order of their
+1 + N(0, 0.02), integer tables uniform, convolution taps uniform in (-1, 1), rates uniform
+in (0, 0.1). Tensors are drawn in the order of their
 sorted names from one seeded CPU generator, so a folder is the same wherever it is
 written. (The reference's only random model is a test fixture: tests/tiny_model.py:21-50.)
 """
@@ -22,9 +23,14 @@ STD = 0.02
 
 
 def draw(spec, generator: torch.Generator, device="cpu") -> torch.Tensor:
+    shape = spec.drawn_shape()
     if spec.kind == "index":
-        return torch.randint(0, max(1, spec.shape[0]), spec.shape, generator=generator, device=device, dtype=torch.int32)
-    t = torch.randn(spec.shape, generator=generator, device=device, dtype=torch.float32) * STD
+        return torch.randint(0, max(1, shape[0]), shape, generator=generator, device=device, dtype=torch.int32)
+    if spec.kind == "taps":
+        return torch.rand(shape, generator=generator, device=device, dtype=torch.float32) * 2.0 - 1.0
+    if spec.kind == "rate":
+        return torch.rand(shape, generator=generator, device=device, dtype=torch.float32) * 0.1
+    t = torch.randn(shape, generator=generator, device=device, dtype=torch.float32) * STD
     return t + 1.0 if spec.kind == "scale" else t
 
 
