@@ -11,7 +11,7 @@
 // u^T S and S^T r are sums over key channels only. So a block owns some value channels of one head
 // of one request, a thread owns a run of key channels of one value channel in registers, and the
 // two sums are reductions over the few neighbouring lanes that share a value channel. Tokens of a
-// portion are taken in tiles: the tile's vectors (w, a u, u, k, r, v) are prepared by all
+// portion are taken in tiles: the tile's vectors (w, a u, u, k, w r, v) are prepared by all
 // threads into shared memory, then the recurrence walks the tile without a block-wide barrier.
 // The state is read at the start of a portion and written back at its end, so a prompt cut into
 // portions, or decoded token by token, computes bit for bit what the whole prompt computes.
@@ -56,8 +56,8 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
   const bool owns = column < p.columns && j < d;
   const int first = p.q_start[e], count = p.q_start[e + 1] - first;
 
-  // per tile token: u, w, au, k, r [dp each], v [columns]
-  const int per_token = 5 * dp + p.columns;
+  // per tile token: u, w, au, k, wr [dp each], v [columns], c1, c2
+  const int per_token = 5 * dp + p.columns + 2;
   float S[RPT];
   float* mine = p.state + (((size_t)p.state_slot[e] * p.heads + h) * d + (owns ? j : 0)) * d;
 #pragma unroll
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
       at[dp + i] = w;
       at[2 * dp + i] = a;                       // times u below
       at[3 * dp + i] = k;
-      at[4 * dp + i] = r;
+      at[4 * dp + i] = r;                       // times w below
     }
     for (int idx = tid; idx < n * p.columns; idx += threads) {
       const int tok = idx / p.columns, c = idx - tok * p.columns;
@@ -93,34 +93,56 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
           (j0 + c < d) ? p.proj[(size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c] : 0.f;
     }
     __syncthreads();
-    for (int tok = warp; tok < n; tok += warps) {        // the unit key: a warp per token
+    // A warp per token: the unit key, and the two sums over key channels that the output needs
+    // beside the old state, c1 = sum(a u r) and c2 = sum(k r). They are where r meets k head
+    // on, so they cancel hardest; they are summed in double and rounded once.
+    for (int tok = warp; tok < n; tok += warps) {
       float* at = smem + (size_t)tok * per_token;
       float squares = 0.f;
       for (int i = lane; i < d; i += 32) squares = fmaf(at[3 * dp + i], at[3 * dp + i], squares);
       const float inv = 1.f / sqrtf(warp_sum(squares) + p.key_eps);
+      double c1 = 0.0, c2 = 0.0;
       for (int i = lane; i < dp; i += 32) {
-        const float u = at[3 * dp + i] * inv;
+        const float k = at[3 * dp + i], r = at[4 * dp + i];
+        const float u = k * inv;
+        const float au = at[2 * dp + i] * u;
         at[i] = u;
-        at[2 * dp + i] *= u;
+        at[2 * dp + i] = au;
+        at[4 * dp + i] = at[dp + i] * r;
+        c1 += (double)au * (double)r;
+        c2 += (double)k * (double)r;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+        c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+      }
+      if (lane == 0) {
+        at[5 * dp + p.columns] = (float)c1;
+        at[5 * dp + p.columns + 1] = (float)c2;
       }
     }
     __syncthreads();
+    // o = S_new^T r written over the old state: sum(w r S_old) - (u^T S_old) c1 + v c2, so that both
+    // sums over the state's registers run side by side and share one round of shuffles.
     for (int tok = 0; tok < n; ++tok) {
       const float* at = smem + (size_t)tok * per_token + part * RPT;
-      float us = 0.f;
-#pragma unroll
-      for (int rr = 0; rr < RPT; ++rr) us = fmaf(at[rr], S[rr], us);
-      for (int o = P >> 1; o > 0; o >>= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
-      const float v = owns ? smem[(size_t)tok * per_token + 5 * dp + column] : 0.f;
-      float out = 0.f;
+      float us = 0.f, rs = 0.f;
 #pragma unroll
       for (int rr = 0; rr < RPT; ++rr) {
-        const float s = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us, at[dp + rr] * S[rr]));
-        S[rr] = s;
-        out = fmaf(s, at[4 * dp + rr], out);
+        us = fmaf(at[rr], S[rr], us);
+        rs = fmaf(at[4 * dp + rr], S[rr], rs);
       }
-      for (int o = P >> 1; o > 0; o >>= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-      if (owns && part == 0) p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = out;
+      for (int o = P >> 1; o > 0; o >>= 1) {
+        us += __shfl_xor_sync(0xffffffffu, us, o);
+        rs += __shfl_xor_sync(0xffffffffu, rs, o);
+      }
+      const float* tail = smem + (size_t)tok * per_token + 5 * dp;
+      const float v = owns ? tail[column] : 0.f;
+#pragma unroll
+      for (int rr = 0; rr < RPT; ++rr) S[rr] = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us, at[dp + rr] * S[rr]));
+      if (owns && part == 0)
+        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[p.columns + 1], fmaf(-us, tail[p.columns], rs));
     }
   }
   if (owns) {
@@ -207,7 +229,7 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, const float* proj, in
   p.heads = heads; p.d = d; p.columns = (d + column_splits - 1) / column_splits;
   p.decay_scale = decay_scale; p.key_eps = key_eps;
   const int dp = P * rpt;
-  const int per_token = 5 * dp + p.columns;
+  const int per_token = 5 * dp + p.columns + 2;
   int tile = 16;
   while (tile > 1 && (size_t)tile * per_token * sizeof(float) > 40 * 1024) tile /= 2;
   p.tile = tile;

@@ -9,7 +9,11 @@
 // Weights are [out, in] row-major as the checkpoint stores them, which is what
 // x . w^T reads (engine/model.py:303-320 of the reference calls F.linear on the same
 // layout). Every output element sums its K products in the same order whatever M is, so
-// a token's result does not depend on what else is in the batch.
+// a token's result does not depend on what else is in the batch. When activations, weights
+// and output are all float32 the K products are summed in double and rounded once: a
+// sequential float32 sum over a long K loses several bits against what a float32 result
+// can hold, and a model whose layers cancel (a recurrent state read out by a near-orthogonal
+// vector) amplifies exactly that.
 #include "common.cuh"
 
 using namespace pae;
@@ -18,7 +22,7 @@ namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 outputs each
 
-template <typename TA, typename TW, typename TO>
+template <typename TA, typename TW, typename TO, typename TAcc>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, const TA* __restrict__ x,
                                                         const TW* __restrict__ w, const float* __restrict__ bias,
                                                         const TO* __restrict__ residual, int M, int N, int K) {
@@ -30,11 +34,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
   const int tx = tid % 16, ty = tid / 16;      // outputs rows ty*4.., cols tx*4..
   const int load_row = tid / 4, load_k = (tid % 4) * 4;
 
-  float acc[TM][TN];
+  TAcc acc[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) acc[i][j] = (TAcc)0;
 
   for (int k0 = 0; k0 < K; k0 += BK) {
     {
@@ -50,15 +54,15 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
-      float a[TM], b[TN];
+      TAcc a[TM], b[TN];
 #pragma unroll
-      for (int i = 0; i < TM; ++i) a[i] = xs[k][ty * TM + i];
+      for (int i = 0; i < TM; ++i) a[i] = (TAcc)xs[k][ty * TM + i];
 #pragma unroll
-      for (int j = 0; j < TN; ++j) b[j] = ws[k][tx * TN + j];
+      for (int j = 0; j < TN; ++j) b[j] = (TAcc)ws[k][tx * TN + j];
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
     }
     __syncthreads();
   }
@@ -71,19 +75,19 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, co
     for (int j = 0; j < TN; ++j) {
       const int n = n0 + tx * TN + j;
       if (n >= N) continue;
-      float v = acc[i][j];
-      if (bias != nullptr) v += bias[n];
-      if (residual != nullptr) v += to_float(residual[(size_t)m * N + n]);
-      out[(size_t)m * N + n] = from_float<TO>(v);
+      TAcc v = acc[i][j];
+      if (bias != nullptr) v += (TAcc)bias[n];
+      if (residual != nullptr) v += (TAcc)to_float(residual[(size_t)m * N + n]);
+      out[(size_t)m * N + n] = from_float<TO>((float)v);
     }
   }
 }
 
-template <typename TA, typename TW, typename TO>
+template <typename TA, typename TW, typename TO, typename TAcc = float>
 int launch(void* out, const void* x, const void* w, const float* bias, const void* residual, int M, int N, int K,
            cudaStream_t s) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  launch_kernel(gemm_simt_kernel<TA, TW, TO>, grid, 256, 0, s, (TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K);
+  launch_kernel(gemm_simt_kernel<TA, TW, TO, TAcc>, grid, 256, 0, s, (TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K);
   return check_launch("linear_simt");
 }
 
@@ -99,7 +103,7 @@ PAE_EXPORT int pae_linear_simt(void* out, const void* x, const void* w, const fl
   using bf = __nv_bfloat16;
   const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;
   switch (key) {
-    case 0: return launch<float, float, float>(out, x, w, bias, residual, M, N, K, s);
+    case 0: return launch<float, float, float, double>(out, x, w, bias, residual, M, N, K, s);
     case 111: return launch<bf, bf, bf>(out, x, w, bias, residual, M, N, K, s);
     case 110: return launch<bf, bf, float>(out, x, w, bias, residual, M, N, K, s);
     case 101: return launch<bf, float, bf>(out, x, w, bias, residual, M, N, K, s);

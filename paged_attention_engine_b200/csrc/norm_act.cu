@@ -9,13 +9,14 @@ using namespace pae;
 
 namespace {
 
-__device__ __forceinline__ float block_sum(float v, float* scratch) {
-  v = warp_sum(v);
+__device__ __forceinline__ double block_sum(double v, double* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = (blockDim.x + 31) >> 5;
   __syncthreads();                       // scratch may still be read from the call before
   if (lane == 0) scratch[warp] = v;
   __syncthreads();
-  float total = 0.f;
+  double total = 0.0;
   for (int i = 0; i < warps; ++i) total += scratch[i];     // every thread adds in the same order
   return total;
 }
@@ -48,17 +49,19 @@ template <typename TI, typename TO>
 __global__ void layer_norm_kernel(TO* __restrict__ out, const TI* __restrict__ x, const float* __restrict__ weight,
                                   const float* __restrict__ bias, int width, float eps) {
   dependent_launch_prologue();
-  __shared__ float scratch[32];
+  __shared__ double scratch[32];
   const TI* row = x + (size_t)blockIdx.x * width;
-  float sum = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) sum += to_float(row[i]);
-  const float mean = block_sum(sum, scratch) / (float)width;
-  float squares = 0.f;
+  // The two sums are double: they cost nothing beside the row's traffic, and the mean and the
+  // variance then carry no error of their own into every element of the row.
+  double sum = 0.0;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) sum += (double)to_float(row[i]);
+  const float mean = (float)(block_sum(sum, scratch) / (double)width);
+  double squares = 0.0;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float dev = to_float(row[i]) - mean;
-    squares = fmaf(dev, dev, squares);
+    const double dev = (double)to_float(row[i]) - (double)mean;
+    squares = fma(dev, dev, squares);
   }
-  const float inv = 1.f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+  const float inv = (float)(1.0 / sqrt(block_sum(squares, scratch) / (double)width + (double)eps));
   TO* to = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = (to_float(row[i]) - mean) * inv * weight[i];
