@@ -56,6 +56,37 @@ def dense_feed_forward(h, up, down):
     return gelu_erf(h @ _f(up).T) @ _f(down).T
 
 
+def scored_attention(q, k, v, scale, temp=None, cap=None, r1=None, r2=None, sink=None, size=None, keep=0, rows=None):
+    """Attention of queries q [T, H, d] over keys k [T, G, d] and values v [T, G, dv] of the same
+    sequence under the score rule; `rows` limits the query positions that are computed (the others
+    stay zero). Returns [T, H, dv]."""
+    T, H, d = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=F)
+    for head in range(H):
+        g = head // (H // G)
+        for i in (range(T) if rows is None else rows):
+            scores, seen = [], []
+            for j in range(i + 1):
+                if size is not None and not (i - j < int(size) or j < keep):
+                    continue
+                s = float(q[i, head] @ k[j, g]) * scale
+                if temp is not None:
+                    s *= float(temp[head])
+                if cap:
+                    s = float(cap) * math.tanh(s / float(cap))
+                if r1 is not None:
+                    s -= float(r1[head]) * math.log(1.0 + float(r2[head]) * (i - j))
+                scores.append(s)
+                seen.append(j)
+            m = max(scores + ([float(sink[head])] if sink is not None else []))
+            weights = [math.exp(s - m) for s in scores]
+            denominator = sum(weights) + (math.exp(float(sink[head]) - m) if sink is not None else 0.0)
+            for wgt, j in zip(weights, seen):
+                out[i, head] += (wgt / denominator) * v[j, g]
+    return out
+
+
 def windowed_sink_attention(h, tensors, prefix, mixer, eps):
     """The attention mixer over one whole sequence h [T, W]."""
     H, G, d = int(mixer["heads"]), int(mixer["kv_heads"]), int(mixer["dim"])
@@ -71,31 +102,10 @@ def windowed_sink_attention(h, tensors, prefix, mixer, eps):
     q = unit_rms(q.view(T, H, d), eps)
     k = unit_rms(k.view(T, G, d), eps)
     v = v.view(T, G, dv)
-    scale = float(mixer["scale"])
-    cap = mixer.get("softcap")
     mask = mixer.get("mask") or {}
-    size = mask.get("size")
-    keep = int(mask.get("keep_first") or 0)
     temp, r1, r2, sink = (_f(tensors[f"{prefix}.{n}"]) for n in ("temp", "r1", "r2", "sink"))
-    out = torch.zeros(T, H, dv, dtype=F)
-    for head in range(H):
-        g = head // (H // G)
-        for i in range(T):
-            scores, seen = [], []
-            for j in range(i + 1):
-                if size is not None and not (i - j < int(size) or j < keep):
-                    continue
-                s = float(q[i, head] @ k[j, g]) * scale * float(temp[head])
-                if cap:
-                    s = float(cap) * math.tanh(s / float(cap))
-                s -= float(r1[head]) * math.log(1.0 + float(r2[head]) * (i - j))
-                scores.append(s)
-                seen.append(j)
-            m = max(scores + [float(sink[head])])
-            weights = [math.exp(s - m) for s in scores]
-            denominator = sum(weights) + math.exp(float(sink[head]) - m)
-            for wgt, j in zip(weights, seen):
-                out[i, head] += (wgt / denominator) * v[j, g]
+    out = scored_attention(q, k, v, float(mixer["scale"]), temp, mixer.get("softcap"), r1, r2, sink,
+                           mask.get("size"), int(mask.get("keep_first") or 0))
     return out.reshape(T, H * dv) @ _f(tensors[f"{prefix}.o"]).T
 
 
