@@ -1,0 +1,254 @@
+// The scored attention rule of attention_scored.cu on tensor cores, for bfloat16: both products
+// are mma.sync m16n8k16 with float32 accumulation (the tile helpers of attention_mma.cuh), the
+// rule is applied to the float32 scores between them:
+//
+//   s = (q . k) * scale * temp[h];  s <- cap * tanh(s / cap);  s <- s - r1[h] * log(1 + r2[h] * (i - j))
+//   seen: j <= i and (no window, or i - j < window, or j < keep_first);  a sink logit per head in the denominator
+//
+// A block owns 64 consecutive query tokens of one request and one head (a single decoded token
+// is a tile with one row) and walks 64 keys at a time over two ranges: the kept first keys, and
+// from the first query's window to the last query. Keys of a tile that no row of the block can
+// see are not read (their pages may have been given back), and 16-key steps that a warp's rows
+// cannot see are skipped. Query/key heads and value heads may have different sizes (32, 64 or
+// 128 each). tanh and the logarithm use the hardware's exp2 and log2 (relative error about
+// 1e-6 on a float32 score); probabilities are rounded to bfloat16 for the second product.
+#include "attention_mma.cuh"
+
+using namespace pae;
+using namespace pae_attention;
+
+namespace {
+
+struct ScoredParams {
+  __nv_bfloat16* out;           // [tokens, heads, DV]
+  const __nv_bfloat16* q;       // [tokens, heads, D]
+  const __nv_bfloat16* keys;    // [pages, kv_heads, page_size, D]
+  const __nv_bfloat16* values;  // [pages, kv_heads, page_size, DV]
+  const int* block_table;
+  const int* q_start;
+  const int* q_pos0;
+  const int* kv_len;
+  int table_width, heads, kv_heads, page_size, window, keep_first;
+  float scale, cap;
+  const float* temp;
+  const float* r1;
+  const float* r2;
+  const float* sink;
+};
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  const float e = fast_exp2(x * (2.f * LOG2E));          // e^(2x); inf and 0 at the ends give +1 and -1
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
+  dependent_launch_prologue();
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int first_token = p.q_start[b];
+  const int q_count = p.q_start[b + 1] - first_token;
+  const int tile = blockIdx.x;
+  if (tile * PREFILL_BQ >= q_count) return;
+  const uint32_t smem_base = smem_u32(smem);
+  const int g = h / (p.heads / p.kv_heads);
+  const int* table = p.block_table + (size_t)b * p.table_width;
+  const int warp_row0 = warp * 16;
+  constexpr int K_BYTES = PREFILL_BKEYS * D * 2, V_BYTES = PREFILL_BKEYS * DV * 2, STAGE_BYTES = K_BYTES + V_BYTES;
+
+  const int rows = min(PREFILL_BQ, q_count - tile * PREFILL_BQ);
+  const int pos0 = p.q_pos0[b] + tile * PREFILL_BQ;
+  const int kv_end = min(p.kv_len[b], pos0 + rows);
+  const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int kv_begin = (first_key / 16) * 16;
+  // Tiles of the kept first keys come first, unless they touch the window's tiles anyway.
+  int kept_end = p.window > 0 ? min(p.keep_first, first_key) : 0;
+  int kept_tiles = (kept_end + PREFILL_BKEYS - 1) / PREFILL_BKEYS;
+  if (kept_tiles * PREFILL_BKEYS > kv_begin) {
+    kv_begin = 0;
+    kept_tiles = 0;
+    kept_end = 0;
+  }
+  const int tiles = kept_tiles + (kv_end - kv_begin + PREFILL_BKEYS - 1) / PREFILL_BKEYS;
+
+  uint32_t q[D / 16][4];
+  load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
+    const int row = warp_row0 + r;
+    return row < rows ? p.q + ((size_t)(first_token + tile * PREFILL_BQ + row) * p.heads + h) * D : nullptr;
+  });
+
+  // Rows of a tile that lie at or beyond `limit` are zero-filled and never seen.
+  auto fetch = [&](int stage, int key0, int limit) {
+    const uint32_t k_dst = smem_base + stage * STAGE_BYTES;
+    for (int i = threadIdx.x; i < PREFILL_BKEYS * (D / 8 + DV / 8); i += 128) {
+      const bool is_key = i < PREFILL_BKEYS * (D / 8);
+      const int local = is_key ? i : i - PREFILL_BKEYS * (D / 8);
+      const int chunks = is_key ? D / 8 : DV / 8;
+      const int row = local / chunks, chunk = local - row * chunks;
+      const int key = key0 + row;
+      const int offset_in_tile = is_key ? TileLayout<D>::offset_bytes(row, chunk) : K_BYTES + TileLayout<DV>::offset_bytes(row, chunk);
+      // Keys before the block's window that are not kept first keys may lie in pages that were given back.
+      if (key < limit && (key >= first_key || key < p.keep_first)) {
+        const int page = checked_page(table[checked_table_index(key / p.page_size, p.table_width)]);
+        const size_t at = ((size_t)page * p.kv_heads + g) * p.page_size + (key % p.page_size);
+        cp_async16(k_dst + offset_in_tile, is_key ? p.keys + at * D + chunk * 8 : p.values + at * DV + chunk * 8);
+      } else {
+        *(uint4*)(smem + stage * STAGE_BYTES + offset_in_tile) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto tile_key0 = [&](int t) { return t < kept_tiles ? t * PREFILL_BKEYS : kv_begin + (t - kept_tiles) * PREFILL_BKEYS; };
+  auto tile_limit = [&](int t) { return t < kept_tiles ? kept_end : kv_end; };
+
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  // Scores are kept in units of log 2. The sink is a logit that is always there: the running
+  // maximum starts at it and the sum at 1.
+  const bool has_sink = p.sink != nullptr;
+  const float sink2 = has_sink ? p.sink[h] * LOG2E : -FLT_MAX;
+  float row_max[2] = {sink2, sink2}, row_sum[2] = {has_sink ? 1.f : 0.f, has_sink ? 1.f : 0.f};
+  const float temp = p.scale * (p.temp != nullptr ? p.temp[h] : 1.f);
+  const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
+  const bool has_bias = p.r1 != nullptr;
+  const float r1 = has_bias ? p.r1[h] : 0.f, r2 = has_bias ? p.r2[h] : 0.f;
+  const int my_pos[2] = {pos0 + warp_row0 + (lane >> 2), pos0 + warp_row0 + (lane >> 2) + 8};
+  const int warp_first_pos = pos0 + warp_row0;
+  const int warp_last_pos = warp_row0 < rows ? pos0 + min(rows, warp_row0 + 16) - 1 : -1;
+  const int c = (lane & 3) * 2;
+
+  if (tiles > 0) fetch(0, tile_key0(0), tile_limit(0));
+  cp_async_commit();
+  for (int t = 0; t < tiles; ++t) {
+    if (t + 1 < tiles) fetch((t + 1) & 1, tile_key0(t + 1), tile_limit(t + 1));
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t k_tile = smem_base + (t & 1) * STAGE_BYTES;
+    const int limit = tile_limit(t);
+#pragma unroll
+    for (int sub = 0; sub < PREFILL_BKEYS / 16; ++sub) {
+      const int key0 = tile_key0(t) + sub * 16;
+      if (key0 > warp_last_pos || key0 >= limit) continue;
+      if (p.window > 0 && key0 + 15 < warp_first_pos - p.window + 1 && key0 >= p.keep_first) continue;
+      float s[2][4];
+      scores_16_keys<D>(s, q, k_tile, sub * 16);
+      float block_max[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int half = j >> 1, key = key0 + u * 8 + c + (j & 1);
+          const int distance = my_pos[half] - key;
+          const bool seen = key < limit && distance >= 0 && (p.window <= 0 || distance < p.window || key < p.keep_first);
+          float x = s[u][j] * temp;
+          if (p.cap > 0.f) x = p.cap * fast_tanh(x * inv_cap);
+          if (has_bias && seen) x -= r1 * __logf(1.f + r2 * (float)distance);
+          s[u][j] = seen ? x * LOG2E : -FLT_MAX;
+          block_max[half] = fmaxf(block_max[half], s[u][j]);
+        }
+      float rescale[2];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        block_max[half] = fmaxf(block_max[half], __shfl_xor_sync(0xffffffffu, block_max[half], 1));
+        block_max[half] = fmaxf(block_max[half], __shfl_xor_sync(0xffffffffu, block_max[half], 2));
+        const float new_max = fmaxf(row_max[half], block_max[half]);
+        rescale[half] = row_max[half] == -FLT_MAX ? 0.f : fast_exp2(row_max[half] - new_max);
+        row_max[half] = new_max;
+      }
+      float block_sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int half = j >> 1;
+          const float e = s[u][j] == -FLT_MAX ? 0.f : fast_exp2(s[u][j] - row_max[half]);
+          s[u][j] = e;
+          block_sum[half] += e;
+        }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        block_sum[half] += __shfl_xor_sync(0xffffffffu, block_sum[half], 1);
+        block_sum[half] += __shfl_xor_sync(0xffffffffu, block_sum[half], 2);
+        row_sum[half] = row_sum[half] * rescale[half] + block_sum[half];
+      }
+      if (__any_sync(0xffffffffu, rescale[0] != 1.f || rescale[1] != 1.f)) {
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) {
+          o[n][0] *= rescale[0];
+          o[n][1] *= rescale[0];
+          o[n][2] *= rescale[1];
+          o[n][3] *= rescale[1];
+        }
+      }
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
+      accumulate_16_keys<DV>(o, pa, k_tile + K_BYTES, sub * 16);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = warp_row0 + (lane >> 2) + half * 8;
+    if (row >= rows) continue;
+    const float inv = row_sum[half] > 0.f ? 1.f / row_sum[half] : 0.f;
+    __nv_bfloat16* out = p.out + ((size_t)(first_token + tile * PREFILL_BQ + row) * p.heads + h) * DV;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n)
+      *(uint32_t*)(out + n * 8 + (lane & 3) * 2) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+  }
+}
+
+template <int D, int DV>
+int launch(const ScoredParams& p, int seqs, int max_q_len, cudaStream_t s) {
+  const size_t bytes = (size_t)2 * PREFILL_BKEYS * (D + DV) * 2;
+  if (int err = allow_smem(scored_kernel<D, DV>, bytes, "paged_attention_scored_mma")) return err;
+  dim3 grid((max_q_len + PREFILL_BQ - 1) / PREFILL_BQ, p.heads, seqs);
+  launch_kernel(scored_kernel<D, DV>, grid, 128, bytes, s, p);
+  return check_launch("paged_attention_scored_mma");
+}
+
+bool size_ok(int d) { return d == 32 || d == 64 || d == 128; }
+
+}  // namespace
+
+// 1 when the tensor-core kernel takes these head sizes.
+PAE_EXPORT int pae_attention_scored_mma_supports(int d, int dv) { return size_ok(d) && size_ok(dv) ? 1 : 0; }
+
+// bfloat16 only; the arguments of pae_paged_attention_scored without the element type.
+PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const void* keys, const void* values,
+                                              const int* block_table, int table_width, const int* q_start,
+                                              const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads,
+                                              int kv_heads, int d, int dv, int page_size, float scale, float cap,
+                                              const float* temp, const float* r1, const float* r2, const float* sink,
+                                              int window, int keep_first, void* stream) {
+  if (seqs == 0 || max_q_len == 0) return 0;
+  if (!pae_attention_scored_mma_supports(d, dv))
+    return fail(2, "paged_attention_scored_mma: head sizes %d and %d are not 32, 64 or 128", d, dv);
+  if (kv_heads < 1 || heads % kv_heads) return fail(2, "paged_attention_scored_mma: %d heads over %d kv heads", heads, kv_heads);
+  if (heads > 65535 || seqs > 65535) return fail(3, "paged_attention_scored_mma: %d heads x %d requests exceed one launch", heads, seqs);
+  if (page_size < 1) return fail(2, "paged_attention_scored_mma: page size %d", page_size);
+  if ((r1 == nullptr) != (r2 == nullptr)) return fail(2, "paged_attention_scored_mma: the distance bias needs both of its constants");
+  if (window < 0 || keep_first < 0) return fail(2, "paged_attention_scored_mma: window %d, kept first keys %d", window, keep_first);
+  if (((uintptr_t)q | (uintptr_t)keys | (uintptr_t)values | (uintptr_t)out) & 15)
+    return fail(2, "paged_attention_scored_mma: an operand does not start on a 16-byte boundary");
+  ScoredParams p{(__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)keys, (const __nv_bfloat16*)values,
+                 block_table, q_start, q_pos0, kv_len, table_width, heads, kv_heads, page_size, window, keep_first,
+                 scale, cap, temp, r1, r2, sink};
+  cudaStream_t s = (cudaStream_t)stream;
+#define PAE_SCORED_CASE(DD, DDV) \
+  if (d == DD && dv == DDV) return launch<DD, DDV>(p, seqs, max_q_len, s);
+  PAE_SCORED_CASE(32, 32) PAE_SCORED_CASE(64, 64) PAE_SCORED_CASE(128, 128)
+  PAE_SCORED_CASE(32, 64) PAE_SCORED_CASE(64, 32) PAE_SCORED_CASE(64, 128) PAE_SCORED_CASE(128, 64)
+  PAE_SCORED_CASE(32, 128) PAE_SCORED_CASE(128, 32)
+#undef PAE_SCORED_CASE
+  return fail(2, "paged_attention_scored_mma: head sizes %d and %d", d, dv);
+}
+
+PAE_DEFINE_LAST_ERROR()

@@ -48,6 +48,7 @@ FAMILIES: dict[str, list[str]] = {
     "norm_act": ["norm_act.cu", "common.cuh"],
     "short_conv": ["short_conv.cu", "common.cuh"],
     "attention_scored": ["attention_scored.cu", "common.cuh"],
+    "attention_scored_mma": ["attention_scored_mma.cu", "attention_mma.cuh", "common.cuh"],
     "delta_rule": ["delta_rule.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",

@@ -925,11 +925,13 @@ def conv_heads_cache_write(proj, taps_weight, state, positions, seq_index, q_sta
 
 def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
                            value_dim, page_size, max_q_len, scale, softcap=0.0, temp=None, r1=None, r2=None, sink=None,
-                           window: int = 0, keep_first: int = 0) -> torch.Tensor:
+                           window: int = 0, keep_first: int = 0, form: str | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages under a score rule:
     (q . k) * scale * temp[h], capped by softcap * tanh(. / softcap), minus r1[h] * log(1 + r2[h] *
     distance), a window that keeps the first `keep_first` keys, and a sink logit per head in the
-    softmax's denominator. temp, r1, r2, sink are float32 [heads] or None. -> [tokens, heads * value_dim]."""
+    softmax's denominator. temp, r1, r2, sink are float32 [heads] or None. -> [tokens, heads * value_dim].
+    bfloat16 with head sizes of 32, 64 or 128 runs on tensor cores (csrc/attention_scored_mma.cu), everything
+    else, and everything when `form` is "simt", on the CUDA cores (csrc/attention_scored.cu)."""
     q = materialized(q)
     _need(q, "paged_attention_scored: q")
     _need(keys, "paged_attention_scored: keys", q.dtype)
@@ -945,6 +947,15 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
     if q.shape[1] != num_heads * head_dim:
         raise KernelError(f"paged_attention_scored: q rows of {q.shape[1]} for {num_heads} heads of {head_dim}")
     out = torch.empty((tokens, num_heads * value_dim), dtype=q.dtype, device=q.device)
+    if (q.dtype == torch.bfloat16 and use_tensor_cores and head_dim in (32, 64, 128) and value_dim in (32, 64, 128)
+            and form != "simt"):
+        lib = _lib("attention_scored_mma")
+        _set_bounds("attention_scored_mma", keys)
+        _check(lib, lib.pae_paged_attention_scored_mma(
+            _ptr(out), _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start),
+            _ptr(q_pos0), _ptr(kv_len), kv_len.numel(), max_q_len, num_heads, num_kv_heads, head_dim, value_dim, page_size,
+            scale, float(softcap or 0.0), _ptr(temp), _ptr(r1), _ptr(r2), _ptr(sink), int(window), int(keep_first), _stream()))
+        return out
     lib = _lib("attention_scored")
     _set_bounds("attention_scored", keys)
     _check(lib, lib.pae_paged_attention_scored(

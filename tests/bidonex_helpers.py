@@ -49,7 +49,14 @@ SMALL_B = config(301, 96, [
 ], eps=1e-6)
 ONLY_DELTA = config(97, 48, [delta(2, 24, 8, ff=64), delta(3, 16, 4)])
 ONLY_ATTENTION = config(97, 48, [attention(4, 2, 12, 20, 0.3, softcap=10.0, conv=3, size=10, keep_first=2, ff=64)])
-SMALL = {"small_a": (SMALL_A, 4, 11), "small_b": (SMALL_B, 16, 12), "only_delta": (ONLY_DELTA, 8, 13),
+# Head sizes that the tensor-core kernels take (32, 64, 128), keys and values of different sizes.
+SMALL_C = config(257, 128, [
+    attention(4, 2, 64, 64, 0.125, softcap=20.0, conv=3, size=24, keep_first=4, ff=256),
+    delta(2, 64, 16, ff=256),
+    attention(2, 1, 32, 128, 0.18, conv=2, size=70, keep_first=2, ff=256),
+    attention(2, 2, 128, 32, 0.09, softcap=30.0),
+])
+SMALL = {"small_c": (SMALL_C, 16, 15), "small_a": (SMALL_A, 4, 11), "small_b": (SMALL_B, 16, 12), "only_delta": (ONLY_DELTA, 8, 13),
          "only_attention": (ONLY_ATTENTION, 4, 14)}       # config, page size, seed
 
 

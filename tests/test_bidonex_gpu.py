@@ -131,7 +131,7 @@ def test_short_convolution_across_portions(dtype):
 
 
 def _attention_case(dtype, T, heads, kv_heads, d, dv, page, rows, size=None, keep=0, cap=None, bias=True, sink=True,
-                    temp=True, stand_out=(), decode=False, seed=0):
+                    temp=True, stand_out=(), decode=False, seed=0, form=None, holes=False):
     """One sequence of T keys in shuffled pages; queries `rows` (all as one prompt, or each as a
     single decoded token over the keys before it). `stand_out` = (query, key) pairs whose score is
     made to dominate, so that the output says whether that key was seen."""
@@ -171,11 +171,14 @@ def _attention_case(dtype, T, heads, kv_heads, d, dv, page, rows, size=None, kee
         out = ops.paged_attention_scored(
             q[first : first + count].reshape(count, heads * d).to(DEV).contiguous(), keys, values, block_table,
             _ints([0, count]), _ints([first]), _ints([first + count]), heads, kv_heads, d, dv, page, count, scale, cap or 0.0,
-            dev["temp"], dev["r1"], dev["r2"], dev["sink"], size or 0, keep)
+            dev["temp"], dev["r1"], dev["r2"], dev["sink"], size or 0, keep, form=form)
         return out.reshape(count, heads, dv)
 
     if decode:
         for i in rows:
+            if holes and size:       # what the cache manager does: pages wholly behind the window are gone, kept ones stay
+                gone = _ints([[-1 if (keep + page - 1) // page <= n < max(i - size + 1, 0) // page else t for n, t in enumerate(table)]])
+                block_table.copy_(gone)
             _close(run(i, 1)[0], want[i], dtype)
     else:
         got = run(0, T)
@@ -214,6 +217,27 @@ def test_attention_rule_pieces_can_be_absent(dtype):
     _attention_case(dtype, 45, 2, 1, 96, 96, 16, rows, cap=5.0, sink=True, bias=False, seed=6)
     _attention_case(dtype, 45, 6, 2, 8, 40, 8, rows, size=9, keep=2, sink=False, seed=7)
     _attention_case(dtype, 3, 1, 1, 7, 5, 2, [0, 1, 2], size=2, keep=1, cap=3.0, seed=8)     # odd head sizes, the first tokens
+
+
+@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("d, dv", [(64, 64), (128, 128), (32, 128), (128, 64)])
+@pytest.mark.parametrize("size, keep, page", [(40, 4, 16), (70, 130, 4), (None, 0, 16), (100, 0, 8)])
+def test_tensor_core_attention_at_the_same_edges(decode, d, dv, size, keep, page):
+    """Head sizes of 32, 64 and 128 in bfloat16 take the tensor-core kernel: the same cases, with pages
+    behind the window taken out of the table as the cache manager does."""
+    T, i = 300, 299
+    rows = [i, i - 1, i - 2, i - 3, 63, 64, 65, 127, 128, 0, 1, 15, 16, 17]
+    stand = [(i, 5), (i - 1, 2)]
+    if size:
+        rows += [size - 1, size, size + 1, keep, keep + 1]
+        stand = [(i, i - size + 1), (i - 1, i - 1 - size)]
+        if keep:
+            stand += [(i - 2, keep - 1), (i - 3, keep)]
+    rows = sorted(set(r for r in rows if 0 <= r < T))
+    _attention_case(torch.bfloat16, T, 4, 2, d, dv, page, rows, size=size, keep=keep, cap=15.0, stand_out=stand,
+                    decode=decode, seed=d + dv, holes=True)
+    _attention_case(torch.bfloat16, T, 4, 2, d, dv, page, rows, size=size, keep=keep, cap=15.0, stand_out=stand,
+                    decode=decode, seed=d + dv, form="simt")
 
 
 # --------------------------------------------------------------------------- #
