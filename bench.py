@@ -246,6 +246,76 @@ def time_prefill(engine, torch, repeats: int = PASSES, tokens: int = PREFILL_TOK
     return summary(times)
 
 
+# --------------------------------------------------------------------------- #
+# Bidonex beside Qwen2 at equal layer sizes (`--only bidonex`): the same width, head count, head
+# size, kv heads, feed-forward width, vocabulary and number of layers; Bidonex alternates a
+# generalized-delta layer and a scored-window-attention layer (window 1,024, 4 kept keys, 4 taps).
+# --------------------------------------------------------------------------- #
+BIDONEX_SIZES = {
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, ff=8960, vocab=151936, layers=8),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, ff=18944, vocab=152064, layers=4),
+}
+
+
+def bidonex_pair(size: dict, window: int = 1024) -> tuple[dict, dict]:
+    """(Bidonex config, Qwen2 config) of equal layer sizes."""
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+        "scale": size["dim"] ** -0.5, "softcap": 30.0, "conv": 4, "mask": {"size": window, "keep_first": 4}}}
+    delta = {"type": "general_delta", "mlp": mlp, "mixer": {"heads": size["heads"], "dim": size["dim"], "rank": 64}}
+    bidonex = {"architecture": "Bidonex", "vocab": size["vocab"], "width": size["width"], "max_positions": 32768,
+               "norm": {"eps": 1e-6}, "layers": [delta if i % 2 == 0 else attention for i in range(size["layers"])]}
+    qwen = dict(MODEL, num_hidden_layers=size["layers"], hidden_size=size["width"], num_attention_heads=size["heads"],
+                num_key_value_heads=size["kv_heads"], head_dim=size["dim"], intermediate_size=size["ff"],
+                vocab_size=size["vocab"], tie_word_embeddings=False)
+    return bidonex, qwen
+
+
+def step_cache_bytes(cache, contexts) -> float:
+    """Cache bytes that a decode step reads: per page group the keys and values a request can see
+    (all of its context, or the window and the kept first keys), and every recurrent state
+    read and written once."""
+    size = cache.pools[0].element_size() if cache.pools else 2
+    total = 0.0
+    for g in cache.plan.groups:
+        per_token = len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * size
+        total += per_token * sum(min(c, g.window + g.keep_first) if g.window else c for c in contexts)
+    for state in cache.states.values():
+        total += 2.0 * len(contexts) * state[0].numel() * state.element_size()
+    return total
+
+
+def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes) -> dict:
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.sampling import SamplingRow
+
+    out: dict = {"only": "bidonex", "peaks": peak["source"], "sizes": {}}
+    for name in sizes:
+        bidonex, qwen = bidonex_pair(BIDONEX_SIZES[name])
+        rows: dict = {}
+        for arch, raw in (("bidonex", bidonex), ("qwen2", qwen)):
+            engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
+            row: dict = {"layers": BIDONEX_SIZES[name]["layers"], "weight_gb": round(engine.weight_bytes() / 1e9, 3)}
+            for tokens in (512, 2048, 8192):
+                t = time_prefill(engine, torch, tokens=tokens)
+                row[f"prefill_{tokens}"] = {"ms": round(t["median"], 3), "tokens_per_s": round(tokens / (t["median"] / 1e3), 1)}
+            for batch, context in ((8, 4096), (64, 4096), (8, 16384)):
+                d = time_decode(engine, batch, steps, warmup, torch, SamplingRow, context=context)
+                cache = engine.new_paged_cache(8, BLOCK_SIZE, 1)
+                read = engine.weight_bytes(batch) + step_cache_bytes(cache, [context] * batch)
+                del cache
+                row[f"decode_b{batch}_ctx{context}"] = {
+                    "ms_per_step": round(d["ms_per_step"], 4), "tokens_per_s": round(d["tokens_per_s"], 1),
+                    "gb_per_step": round(read / 1e9, 3),
+                    "hbm_frac": round(read / (d["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4), "launches": d["launches"]}
+            rows[arch] = row
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][name] = rows
+    return out
+
+
 def time_products(model: dict, tokens: int, torch, peak: dict, copies: int = 28) -> list[dict]:
     """The four matrix products of a decoder layer for a step of `tokens` tokens, with what a step
     runs around them (norm before, rotation and page write, SiLU x up, residual after), each
@@ -658,7 +728,9 @@ def main() -> int:
                         help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
     parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
-    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b"), default="all",
+    parser.add_argument("--arch", choices=("qwen2", "bidonex"), default="qwen2",
+                        help="with --only decode / prefill: the architecture that runs at the --shape's layer sizes")
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
@@ -687,6 +759,10 @@ def main() -> int:
     if args.only == "pressure32b":
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
         return 0
+    if args.only == "bidonex":
+        sizes = ("1.5b", "7b") if args.shape == "1.5b" else (args.shape,)
+        print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes)))
+        return 0
     if args.only == "products":
         for row in time_products({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape], args.batch, torch, peak):
             print(json.dumps(row))
@@ -696,7 +772,18 @@ def main() -> int:
     if args.only != "all" and args.shape != "1.5b" and args.layers == MODEL["num_hidden_layers"]:
         args.layers = model["num_hidden_layers"]
     model["num_hidden_layers"] = args.layers
-    engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
+    if args.arch == "bidonex" and args.only in ("decode", "prefill"):
+        if args.shape not in BIDONEX_SIZES:
+            print(f"bench.py: --arch bidonex has the shapes {', '.join(BIDONEX_SIZES)}")
+            return 2
+        size = dict(BIDONEX_SIZES[args.shape])
+        if args.layers != MODEL["num_hidden_layers"]:
+            size["layers"] = args.layers
+        args.layers = size["layers"]
+        bidonex, model = bidonex_pair(size)
+        engine = Engine.from_random(bidonex, seed=0, dtype="bfloat16", device="cuda:0")
+    else:
+        engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
 
     if args.only == "prefill":
         prefill = time_prefill(engine, torch, tokens=args.tokens)

@@ -78,24 +78,46 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
     return row < rows ? p.q + ((size_t)(first_token + tile * PREFILL_BQ + row) * p.heads + h) * D : nullptr;
   });
 
-  // Rows of a tile that lie at or beyond `limit` are zero-filled and never seen.
+  // Rows of a tile that lie at or beyond `limit` are zero-filled and never seen. A thread copies the
+  // same 16-byte column of a few rows in every tile. The rows' pages are looked up first, all of
+  // them, and the copies issued afterwards: one trip to memory for the lookups instead of one per row.
+  constexpr int K_CHUNKS = D / 8, V_CHUNKS = DV / 8;
+  constexpr int K_ROWS = 128 / K_CHUNKS, V_ROWS = 128 / V_CHUNKS;               // rows that one pass of the block covers
+  constexpr int K_PER = PREFILL_BKEYS / K_ROWS, V_PER = PREFILL_BKEYS / V_ROWS;
+  const int k_chunk = threadIdx.x % K_CHUNKS, k_row = threadIdx.x / K_CHUNKS;
+  const int v_chunk = threadIdx.x % V_CHUNKS, v_row = threadIdx.x / V_CHUNKS;
+  const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
+  auto row_of = [&](int key, int limit) -> long long {      // row of the key in the pool, -1: not to be read
+    // Keys before the block's window that are not kept first keys may lie in pages that were given back.
+    if (key >= limit || (key < first_key && key >= p.keep_first)) return -1;
+    const int index = page_shift >= 0 ? key >> page_shift : key / p.page_size;
+    const int offset = page_shift >= 0 ? key & (p.page_size - 1) : key - index * p.page_size;
+    const int page = checked_page(table[checked_table_index(index, p.table_width)]);
+    return ((long long)page * p.kv_heads + g) * p.page_size + offset;
+  };
   auto fetch = [&](int stage, int key0, int limit) {
     const uint32_t k_dst = smem_base + stage * STAGE_BYTES;
-    for (int i = threadIdx.x; i < PREFILL_BKEYS * (D / 8 + DV / 8); i += 128) {
-      const bool is_key = i < PREFILL_BKEYS * (D / 8);
-      const int local = is_key ? i : i - PREFILL_BKEYS * (D / 8);
-      const int chunks = is_key ? D / 8 : DV / 8;
-      const int row = local / chunks, chunk = local - row * chunks;
-      const int key = key0 + row;
-      const int offset_in_tile = is_key ? TileLayout<D>::offset_bytes(row, chunk) : K_BYTES + TileLayout<DV>::offset_bytes(row, chunk);
-      // Keys before the block's window that are not kept first keys may lie in pages that were given back.
-      if (key < limit && (key >= first_key || key < p.keep_first)) {
-        const int page = checked_page(table[checked_table_index(key / p.page_size, p.table_width)]);
-        const size_t at = ((size_t)page * p.kv_heads + g) * p.page_size + (key % p.page_size);
-        cp_async16(k_dst + offset_in_tile, is_key ? p.keys + at * D + chunk * 8 : p.values + at * DV + chunk * 8);
-      } else {
+    long long k_at[K_PER];
+#pragma unroll
+    for (int j = 0; j < K_PER; ++j) k_at[j] = row_of(key0 + k_row + j * K_ROWS, limit);
+#pragma unroll
+    for (int j = 0; j < K_PER; ++j) {
+      const int offset_in_tile = TileLayout<D>::offset_bytes(k_row + j * K_ROWS, k_chunk);
+      if (k_at[j] >= 0)
+        cp_async16(k_dst + offset_in_tile, p.keys + (size_t)k_at[j] * D + k_chunk * 8);
+      else
         *(uint4*)(smem + stage * STAGE_BYTES + offset_in_tile) = make_uint4(0, 0, 0, 0);
-      }
+    }
+    long long v_at[V_PER];
+#pragma unroll
+    for (int j = 0; j < V_PER; ++j) v_at[j] = (D == DV) ? k_at[j] : row_of(key0 + v_row + j * V_ROWS, limit);
+#pragma unroll
+    for (int j = 0; j < V_PER; ++j) {
+      const int offset_in_tile = K_BYTES + TileLayout<DV>::offset_bytes(v_row + j * V_ROWS, v_chunk);
+      if (v_at[j] >= 0)
+        cp_async16(k_dst + offset_in_tile, p.values + (size_t)v_at[j] * DV + v_chunk * 8);
+      else
+        *(uint4*)(smem + stage * STAGE_BYTES + offset_in_tile) = make_uint4(0, 0, 0, 0);
     }
   };
   auto tile_key0 = [&](int t) { return t < kept_tiles ? t * PREFILL_BKEYS : kv_begin + (t - kept_tiles) * PREFILL_BKEYS; };

@@ -10,9 +10,10 @@
 // Both terms read the old state. A column of S (one value channel) never meets another column:
 // u^T S and S^T r are sums over key channels only. So a block owns some value channels of one head
 // of one request, a thread owns a run of key channels of one value channel in registers, and the
-// two sums are reductions over the few neighbouring lanes that share a value channel. Tokens of a
-// portion are taken in tiles: the tile's vectors (w, a u, u, k, w r, v) are prepared by all
-// threads into shared memory, then the recurrence walks the tile without a block-wide barrier.
+// two sums are reductions over the few neighbouring lanes that share a value channel. A first
+// kernel prepares every token's vectors (w, a u, u, k, w r) once per head, in parallel over the
+// tokens; the recurrence then takes a portion's tokens in tiles that asynchronous copies bring
+// into shared memory one tile ahead, and walks a tile without a block-wide barrier.
 // The state is read at the start of a portion and written back at its end, so a prompt cut into
 // portions, or decoded token by token, computes bit for bit what the whole prompt computes.
 //
@@ -32,16 +33,68 @@ struct DeltaParams {
   const float* w_pre;      // [tokens, heads * d]: w~
   const float* w0;         // [heads * d]
   const float* a_bias;     // [heads * d]
+  float* prepared;         // [tokens, heads, 5 d + 2]: u, w, a u, k, w r, c1, c2
   float* state;            // [slots, heads, d (value channel), d (key channel)]
   float* o;                // [tokens, heads * d]
   const int* q_start;      // [entries + 1]
   const int* state_slot;   // [entries]
-  int heads, d, columns;   // columns: value channels per block
-  int tile;                // tokens prepared at a time
+  int tokens, heads, d, columns;   // columns: value channels per block
+  int tile;                // tokens in shared memory at a time (twice: the tile after is on its way)
   float decay_scale, key_eps;
 };
 
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
+
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// What the recurrence needs of a token, once per (token, head), by one warp: the decay w, the unit
+// key u, a u, k, w r, and the two sums over key channels that the output needs beside the old
+// state, c1 = sum(a u r) and c2 = sum(k r). Those two are where r meets k head on, so they
+// cancel hardest; they are summed in double and rounded once.
+__global__ void delta_prepare_kernel(DeltaParams p) {
+  dependent_launch_prologue();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= p.tokens * p.heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = unit / p.heads, h = unit - t * p.heads, d = p.d;
+  const float* row = p.proj + (size_t)t * p.ld;
+  float* out = p.prepared + (size_t)unit * (5 * d + 2);
+  float squares = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float k = row[p.k_off + h * d + i];
+    squares = fmaf(k, k, squares);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(squares) + p.key_eps);
+  double c1 = 0.0, c2 = 0.0;
+  for (int i = lane; i < d; i += 32) {
+    const int c = h * d + i;
+    const float k = row[p.k_off + c], r = row[p.r_off + c];
+    const float a = sigmoidf(row[p.a_off + c] + p.a_bias[c]);
+    const float w = expf(-p.decay_scale * sigmoidf(p.w_pre[(size_t)t * p.heads * d + c] + p.w0[c]));
+    const float u = k * inv, au = a * u;
+    out[i] = u;
+    out[d + i] = w;
+    out[2 * d + i] = au;
+    out[3 * d + i] = k;
+    out[4 * d + i] = w * r;
+    c1 += (double)au * (double)r;
+    c2 += (double)k * (double)r;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+    c2 += __shfl_xor_sync(0xffffffffu, c2, o);
+  }
+  if (lane == 0) {
+    out[5 * d] = (float)c1;
+    out[5 * d + 1] = (float)c2;
+  }
+}
 
 // RPT key channels per thread, P threads per value channel (a power of two of at most 32).
 template <int RPT>
@@ -56,8 +109,10 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
   const bool owns = column < p.columns && j < d;
   const int first = p.q_start[e], count = p.q_start[e + 1] - first;
 
-  // per tile token: u, w, au, k, wr [dp each], v [columns], c1, c2
+  // per tile token: u, w, au, k, wr [dp each], v [columns], c1, c2; two tiles take turns
   const int per_token = 5 * dp + p.columns + 2;
+  const int tile_floats = p.tile * per_token;
+  for (int i = tid; i < 2 * tile_floats; i += threads) smem[i] = 0.f;      // the padding stays zero
   float S[RPT];
   float* mine = p.state + (((size_t)p.state_slot[e] * p.heads + h) * d + (owns ? j : 0)) * d;
 #pragma unroll
@@ -65,86 +120,59 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
     const int i = part * RPT + rr;
     S[rr] = (owns && i < d) ? mine[i] : 0.f;
   }
+  __syncthreads();
 
-  const int lane = tid & 31, warp = tid >> 5, warps = threads >> 5;
-  for (int t0 = 0; t0 < count; t0 += p.tile) {
+  const int source_floats = 5 * d + 2;
+  auto fetch = [&](int t0, float* to) {
     const int n = min(p.tile, count - t0);
-    __syncthreads();                            // the tile before is no longer read
-    for (int idx = tid; idx < n * dp; idx += threads) {
-      const int tok = idx / dp, i = idx - tok * dp;
-      float* at = smem + (size_t)tok * per_token;
-      float k = 0.f, r = 0.f, w = 0.f, a = 0.f;
-      if (i < d) {
-        const float* row = p.proj + (size_t)(first + t0 + tok) * p.ld;
-        const int c = h * d + i;
-        k = row[p.k_off + c];
-        r = row[p.r_off + c];
-        a = sigmoidf(row[p.a_off + c] + p.a_bias[c]);
-        w = expf(-p.decay_scale * sigmoidf(p.w_pre[(size_t)(first + t0 + tok) * p.heads * d + c] + p.w0[c]));
-      }
-      at[dp + i] = w;
-      at[2 * dp + i] = a;                       // times u below
-      at[3 * dp + i] = k;
-      at[4 * dp + i] = r;                       // times w below
+    for (int idx = tid; idx < n * source_floats; idx += threads) {
+      const int tok = idx / source_floats, at = idx - tok * source_floats;
+      const int section = at / d, i = at - section * d;
+      float* dst = to + (size_t)tok * per_token + (section < 5 ? section * dp + i : 5 * dp + p.columns + i);
+      copy_async4(dst, p.prepared + ((size_t)(first + t0 + tok) * p.heads + h) * source_floats + at);
     }
     for (int idx = tid; idx < n * p.columns; idx += threads) {
       const int tok = idx / p.columns, c = idx - tok * p.columns;
-      smem[(size_t)tok * per_token + 5 * dp + c] =
-          (j0 + c < d) ? p.proj[(size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c] : 0.f;
+      if (j0 + c < d)
+        copy_async4(to + (size_t)tok * per_token + 5 * dp + c, p.proj + (size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c);
     }
+  };
+
+  if (count > 0) fetch(0, smem);
+  copy_async_commit();
+  int turn = 0;
+  for (int t0 = 0; t0 < count; t0 += p.tile, turn ^= 1) {
+    const int n = min(p.tile, count - t0);
+    if (t0 + p.tile < count) fetch(t0 + p.tile, smem + (turn ^ 1) * tile_floats);
+    copy_async_commit();
+    copy_async_wait<1>();
     __syncthreads();
-    // A warp per token: the unit key, and the two sums over key channels that the output needs
-    // beside the old state, c1 = sum(a u r) and c2 = sum(k r). They are where r meets k head
-    // on, so they cancel hardest; they are summed in double and rounded once.
-    for (int tok = warp; tok < n; tok += warps) {
-      float* at = smem + (size_t)tok * per_token;
-      float squares = 0.f;
-      for (int i = lane; i < d; i += 32) squares = fmaf(at[3 * dp + i], at[3 * dp + i], squares);
-      const float inv = 1.f / sqrtf(warp_sum(squares) + p.key_eps);
-      double c1 = 0.0, c2 = 0.0;
-      for (int i = lane; i < dp; i += 32) {
-        const float k = at[3 * dp + i], r = at[4 * dp + i];
-        const float u = k * inv;
-        const float au = at[2 * dp + i] * u;
-        at[i] = u;
-        at[2 * dp + i] = au;
-        at[4 * dp + i] = at[dp + i] * r;
-        c1 += (double)au * (double)r;
-        c2 += (double)k * (double)r;
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        c1 += __shfl_xor_sync(0xffffffffu, c1, o);
-        c2 += __shfl_xor_sync(0xffffffffu, c2, o);
-      }
-      if (lane == 0) {
-        at[5 * dp + p.columns] = (float)c1;
-        at[5 * dp + p.columns + 1] = (float)c2;
-      }
-    }
-    __syncthreads();
+    const float* tile = smem + turn * tile_floats;
     // o = S_new^T r written over the old state: sum(w r S_old) - (u^T S_old) c1 + v c2, so that both
     // sums over the state's registers run side by side and share one round of shuffles.
     for (int tok = 0; tok < n; ++tok) {
-      const float* at = smem + (size_t)tok * per_token + part * RPT;
-      float us = 0.f, rs = 0.f;
+      const float* at = tile + (size_t)tok * per_token + part * RPT;
+      float us[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int rr = 0; rr < RPT; ++rr) {
-        us = fmaf(at[rr], S[rr], us);
-        rs = fmaf(at[4 * dp + rr], S[rr], rs);
+        us[rr & 3] = fmaf(at[rr], S[rr], us[rr & 3]);
+        rs[rr & 3] = fmaf(at[4 * dp + rr], S[rr], rs[rr & 3]);
       }
+      float us_all = (us[0] + us[1]) + (us[2] + us[3]), rs_all = (rs[0] + rs[1]) + (rs[2] + rs[3]);
       for (int o = P >> 1; o > 0; o >>= 1) {
-        us += __shfl_xor_sync(0xffffffffu, us, o);
-        rs += __shfl_xor_sync(0xffffffffu, rs, o);
+        us_all += __shfl_xor_sync(0xffffffffu, us_all, o);
+        rs_all += __shfl_xor_sync(0xffffffffu, rs_all, o);
       }
-      const float* tail = smem + (size_t)tok * per_token + 5 * dp;
+      const float* tail = tile + (size_t)tok * per_token + 5 * dp;
       const float v = owns ? tail[column] : 0.f;
 #pragma unroll
-      for (int rr = 0; rr < RPT; ++rr) S[rr] = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us, at[dp + rr] * S[rr]));
+      for (int rr = 0; rr < RPT; ++rr) S[rr] = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us_all, at[dp + rr] * S[rr]));
       if (owns && part == 0)
-        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[p.columns + 1], fmaf(-us, tail[p.columns], rs));
+        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[p.columns + 1], fmaf(-us_all, tail[p.columns], rs_all));
     }
+    __syncthreads();                              // the tile is read; the fetch after next may refill it
   }
+  copy_async_wait<0>();
   if (owns) {
 #pragma unroll
     for (int rr = 0; rr < RPT; ++rr) {
@@ -212,12 +240,13 @@ PAE_EXPORT int pae_delta_rule_layout(int d, int* threads_per_column) {
 
 // proj float32 [tokens, ld] holds r, k, v, a~ at the given column offsets (heads * d columns each);
 // w_pre float32 [tokens, heads * d]; state float32 [slots, heads, d, d] (value channel major);
-// o float32 [tokens, heads * d]. `column_splits` blocks share a head's value channels.
-PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, const float* proj, int ld, int r_off, int k_off, int v_off,
-                                   int a_off, const float* w_pre, const float* w0, const float* a_bias,
-                                   const int* q_start, const int* state_slot, int entries, int heads, int d,
+// o float32 [tokens, heads * d]; prepared float32 scratch of tokens * heads * (5 d + 2).
+// `column_splits` blocks share a head's value channels.
+PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, const float* proj, int ld, int r_off, int k_off,
+                                   int v_off, int a_off, const float* w_pre, const float* w0, const float* a_bias,
+                                   const int* q_start, const int* state_slot, int tokens, int entries, int heads, int d,
                                    int column_splits, float decay_scale, float key_eps, void* stream) {
-  if (entries == 0) return 0;
+  if (entries == 0 || tokens == 0) return 0;
   int P = 0;
   const int rpt = pae_delta_rule_layout(d, &P);
   if (rpt == 0) return fail(2, "delta_rule_scan: head size %d is outside [1, 256]", d);
@@ -225,18 +254,22 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, const float* proj, in
   if (column_splits < 1 || column_splits > d) return fail(2, "delta_rule_scan: %d blocks for %d value channels", column_splits, d);
   DeltaParams p{};
   p.proj = proj; p.ld = ld; p.r_off = r_off; p.k_off = k_off; p.v_off = v_off; p.a_off = a_off;
-  p.w_pre = w_pre; p.w0 = w0; p.a_bias = a_bias; p.state = state; p.o = o; p.q_start = q_start; p.state_slot = state_slot;
-  p.heads = heads; p.d = d; p.columns = (d + column_splits - 1) / column_splits;
+  p.w_pre = w_pre; p.w0 = w0; p.a_bias = a_bias; p.prepared = prepared; p.state = state; p.o = o;
+  p.q_start = q_start; p.state_slot = state_slot;
+  p.tokens = tokens; p.heads = heads; p.d = d; p.columns = (d + column_splits - 1) / column_splits;
   p.decay_scale = decay_scale; p.key_eps = key_eps;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long units = (long long)tokens * heads;
+  launch_kernel(delta_prepare_kernel, (unsigned)((units + 3) / 4), 128, 0, s, p);
+  if (int err = check_launch("delta_rule_prepare")) return err;
   const int dp = P * rpt;
   const int per_token = 5 * dp + p.columns + 2;
   int tile = 16;
-  while (tile > 1 && (size_t)tile * per_token * sizeof(float) > 40 * 1024) tile /= 2;
+  while (tile > 1 && (size_t)2 * tile * per_token * sizeof(float) > 44 * 1024) tile /= 2;
   p.tile = tile;
-  const size_t bytes = (size_t)tile * per_token * sizeof(float);
+  const size_t bytes = (size_t)2 * tile * per_token * sizeof(float);
   const int threads = (p.columns * P + 31) / 32 * 32;
   dim3 grid(entries, heads, (d + p.columns - 1) / p.columns);
-  cudaStream_t s = (cudaStream_t)stream;
   switch (rpt) {
     case 8: launch_kernel(delta_scan_kernel<8>, grid, threads, bytes, s, p, P); break;
     case 16: launch_kernel(delta_scan_kernel<16>, grid, threads, bytes, s, p, P); break;

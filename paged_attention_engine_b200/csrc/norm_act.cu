@@ -70,19 +70,81 @@ __global__ void layer_norm_kernel(TO* __restrict__ out, const TI* __restrict__ x
   }
 }
 
+__device__ __forceinline__ float gelu_of(float z, int kind) {
+  if (kind == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
 // kind 0: 0.5 z (1 + erf(z / sqrt 2)); kind 1: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 template <typename T>
 __global__ void gelu_kernel(T* __restrict__ out, const T* __restrict__ x, long long total, int kind) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const float z = to_float(x[i]);
-  float y;
-  if (kind == 0)
-    y = 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
-  else
-    y = 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-  out[i] = from_float<T>(y);
+  out[i] = from_float<T>(gelu_of(to_float(x[i]), kind));
+}
+
+// bfloat16, eight elements per thread, 16-byte accesses.
+__global__ void gelu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, long long chunks, int kind) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= chunks) return;
+  const uint4 in = *(const uint4*)(x + i * 8);
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&in;
+  uint4 packed;
+  __nv_bfloat162* o = (__nv_bfloat162*)&packed;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    o[e] = __floats2bfloat162_rn(gelu_of(f.x, kind), gelu_of(f.y, kind));
+  }
+  *(uint4*)(out + i * 8) = packed;
+}
+
+// LayerNorm of float32 rows whose width is a multiple of 4: the row is read once, 16 bytes at a
+// time, and stays in registers between the sums and the write. Up to 4 * PER * blockDim columns.
+template <typename TO, int PER>
+__global__ void layer_norm_f32x4_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ weight,
+                                        const float* __restrict__ bias, int width, float eps) {
+  dependent_launch_prologue();
+  __shared__ double scratch[32];
+  const int quads = width >> 2;
+  const float4* row = (const float4*)(x + (size_t)blockIdx.x * width);
+  float4 held[PER];
+  double sum = 0.0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    held[j] = c < quads ? row[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) sum += ((double)held[j].x + (double)held[j].y) + ((double)held[j].z + (double)held[j].w);
+  const float mean = (float)(block_sum(sum, scratch) / (double)width);
+  double squares = 0.0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (threadIdx.x + j * blockDim.x < quads) {
+      const double a = (double)held[j].x - (double)mean, b = (double)held[j].y - (double)mean;
+      const double c = (double)held[j].z - (double)mean, d = (double)held[j].w - (double)mean;
+      squares += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  const float inv = (float)(1.0 / sqrt(block_sum(squares, scratch) / (double)width + (double)eps));
+  TO* to = out + (size_t)blockIdx.x * width;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < quads) {
+      const float4 w = *(const float4*)(weight + 4 * c);
+      const float4 b = bias != nullptr ? *(const float4*)(bias + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float v0 = (held[j].x - mean) * inv * w.x + b.x, v1 = (held[j].y - mean) * inv * w.y + b.y;
+      const float v2 = (held[j].z - mean) * inv * w.z + b.z, v3 = (held[j].w - mean) * inv * w.w + b.w;
+      to[4 * c] = from_float<TO>(v0);
+      to[4 * c + 1] = from_float<TO>(v1);
+      to[4 * c + 2] = from_float<TO>(v2);
+      to[4 * c + 3] = from_float<TO>(v3);
+    }
+  }
 }
 
 int row_threads(int width) { return width >= 2048 ? 512 : (width >= 1024 ? 256 : (width >= 256 ? 128 : 64)); }
@@ -116,6 +178,22 @@ PAE_EXPORT int pae_layer_norm(void* out, const void* x, const float* weight, con
   const int threads = row_threads(width);
   using bf = __nv_bfloat16;
   const int key = in_dtype * 10 + out_dtype;
+  if (in_dtype == kF32 && width % 4 == 0 && width <= 4 * 4 * 256 &&
+      (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)bias) & 15) == 0 && (out_dtype == kF32 || out_dtype == kBF16)) {
+    const int quads = width / 4;
+    const int block = quads <= 64 ? 64 : (quads <= 128 ? 128 : 256);
+    const int per = (quads + block - 1) / block;
+    if (out_dtype == kF32) {
+      if (per <= 1) launch_kernel(layer_norm_f32x4_kernel<float, 1>, rows, block, 0, s, (float*)out, (const float*)x, weight, bias, width, eps);
+      else if (per <= 2) launch_kernel(layer_norm_f32x4_kernel<float, 2>, rows, block, 0, s, (float*)out, (const float*)x, weight, bias, width, eps);
+      else launch_kernel(layer_norm_f32x4_kernel<float, 4>, rows, block, 0, s, (float*)out, (const float*)x, weight, bias, width, eps);
+    } else {
+      if (per <= 1) launch_kernel(layer_norm_f32x4_kernel<bf, 1>, rows, block, 0, s, (bf*)out, (const float*)x, weight, bias, width, eps);
+      else if (per <= 2) launch_kernel(layer_norm_f32x4_kernel<bf, 2>, rows, block, 0, s, (bf*)out, (const float*)x, weight, bias, width, eps);
+      else launch_kernel(layer_norm_f32x4_kernel<bf, 4>, rows, block, 0, s, (bf*)out, (const float*)x, weight, bias, width, eps);
+    }
+    return check_launch("layer_norm");
+  }
   if (key == 0)
     launch_kernel(layer_norm_kernel<float, float>, rows, threads, 0, s, (float*)out, (const float*)x, weight, bias, width, eps);
   else if (key == 1)
@@ -133,6 +211,11 @@ PAE_EXPORT int pae_gelu(void* out, const void* x, long long total, int kind, int
   if (total == 0) return 0;
   if (kind != 0 && kind != 1) return fail(2, "gelu: kind %d (0: erf, 1: tanh)", kind);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kBF16 && total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+    const long long chunks = total / 8;
+    launch_kernel(gelu_bf16x8_kernel, (unsigned)((chunks + 255) / 256), 256, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, chunks, kind);
+    return check_launch("gelu");
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == kF32)
     launch_kernel(gelu_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)x, total, kind);

@@ -1022,12 +1022,14 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
     # (the recurrence of a value channel needs no other), at least a warp's worth of threads each.
     splits, sms = 1, _sm_count(proj.device)
     while (num_seqs * num_heads * splits < sms and head_dim % (2 * splits) == 0
-           and (head_dim // (2 * splits)) * per_column.value >= 64):
+           and (head_dim // (2 * splits)) * per_column.value >= 128):
         splits *= 2
     o = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
-    _check(lib, lib.pae_delta_rule_scan(_ptr(o), _ptr(state), _ptr(proj), ld, offsets[0], offsets[1], offsets[2], offsets[3],
-                                        _ptr(w_pre), _ptr(w0), _ptr(a_bias), _ptr(q_start), _ptr(state_slot), num_seqs,
-                                        num_heads, head_dim, splits, decay_scale, key_eps, _stream()))
+    prepared = torch.empty(tokens * num_heads * (5 * head_dim + 2), dtype=torch.float32, device=proj.device)
+    _check(lib, lib.pae_delta_rule_scan(_ptr(o), _ptr(state), _ptr(prepared), _ptr(proj), ld, offsets[0], offsets[1],
+                                        offsets[2], offsets[3], _ptr(w_pre), _ptr(w0), _ptr(a_bias), _ptr(q_start),
+                                        _ptr(state_slot), tokens, num_seqs, num_heads, head_dim, splits, decay_scale, key_eps,
+                                        _stream()), 2)
     out = torch.empty((tokens, width), dtype=out_dtype, device=proj.device)
     _check(lib, lib.pae_delta_rule_output(_ptr(out), _ptr(o), proj.data_ptr() + 4 * gate_offset, ld, _ptr(norm_weight), tokens,
                                           num_heads, head_dim, norm_eps, _DTYPE_CODE[out_dtype], _stream()))
