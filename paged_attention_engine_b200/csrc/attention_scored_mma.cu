@@ -34,6 +34,12 @@ struct ScoredParams {
   const float* r1;
   const float* r2;
   const float* sink;
+  // Requests that bring one token can have their keys shared out over `splits` blocks, which leave
+  // unnormalised outputs with their maxima and sums for the merge kernel.
+  int splits;
+  float* part_out;              // [requests, heads, splits, DV]
+  float* part_max;              // [requests, heads, splits]  (in units of log 2)
+  float* part_sum;              // [requests, heads, splits]
 };
 
 __device__ __forceinline__ float fast_tanh(float x) {
@@ -49,8 +55,10 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   const int h = blockIdx.y, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
-  const int tile = blockIdx.x;
-  if (tile * PREFILL_BQ >= q_count) return;
+  const bool shared_out = p.splits > 1 && q_count == 1;
+  const int tile = shared_out ? 0 : blockIdx.x;
+  const int split = shared_out ? blockIdx.x : 0;
+  if (shared_out ? split >= p.splits : tile * PREFILL_BQ >= q_count) return;
   const uint32_t smem_base = smem_u32(smem);
   const int g = h / (p.heads / p.kv_heads);
   const int* table = p.block_table + (size_t)b * p.table_width;
@@ -129,8 +137,8 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   // Scores are kept in units of log 2. The sink is a logit that is always there: the running
   // maximum starts at it and the sum at 1.
   const bool has_sink = p.sink != nullptr;
-  const float sink2 = has_sink ? p.sink[h] * LOG2E : -FLT_MAX;
-  float row_max[2] = {sink2, sink2}, row_sum[2] = {has_sink ? 1.f : 0.f, has_sink ? 1.f : 0.f};
+  const float sink2 = has_sink && !shared_out ? p.sink[h] * LOG2E : -FLT_MAX;          // the merge adds it otherwise
+  float row_max[2] = {sink2, sink2}, row_sum[2] = {sink2 != -FLT_MAX ? 1.f : 0.f, sink2 != -FLT_MAX ? 1.f : 0.f};
   const float temp = p.scale * (p.temp != nullptr ? p.temp[h] : 1.f);
   const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
   const bool has_bias = p.r1 != nullptr;
@@ -140,10 +148,16 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   const int warp_last_pos = warp_row0 < rows ? pos0 + min(rows, warp_row0 + 16) - 1 : -1;
   const int c = (lane & 3) * 2;
 
-  if (tiles > 0) fetch(0, tile_key0(0), tile_limit(0));
+  int t_begin = 0, t_end = tiles;
+  if (shared_out) {
+    const int each = (tiles + p.splits - 1) / p.splits;
+    t_begin = min(tiles, split * each);
+    t_end = min(tiles, t_begin + each);
+  }
+  if (t_begin < t_end) fetch(t_begin & 1, tile_key0(t_begin), tile_limit(t_begin));
   cp_async_commit();
-  for (int t = 0; t < tiles; ++t) {
-    if (t + 1 < tiles) fetch((t + 1) & 1, tile_key0(t + 1), tile_limit(t + 1));
+  for (int t = t_begin; t < t_end; ++t) {
+    if (t + 1 < t_end) fetch((t + 1) & 1, tile_key0(t + 1), tile_limit(t + 1));
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -215,6 +229,21 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   }
   cp_async_wait<0>();
 
+  if (shared_out) {               // the one row is row 0 of warp 0: lanes 0..3, first half
+    if (warp == 0 && lane < 4) {
+      const size_t at = ((size_t)b * p.heads + h) * p.splits + split;
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n) {
+        p.part_out[at * DV + n * 8 + lane * 2] = o[n][0];
+        p.part_out[at * DV + n * 8 + lane * 2 + 1] = o[n][1];
+      }
+      if (lane == 0) {
+        p.part_max[at] = row_max[0];
+        p.part_sum[at] = row_sum[0];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int row = warp_row0 + (lane >> 2) + half * 8;
@@ -227,13 +256,41 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   }
 }
 
+// out[token of a single-token request, head, :] from the partial results of its blocks, in their
+// order, with the sink's logit in the denominator.
+__global__ void scored_merge_kernel(const ScoredParams p, int dv) {
+  dependent_launch_prologue();
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int first_token = p.q_start[b];
+  if (p.q_start[b + 1] - first_token != 1) return;
+  const size_t at = ((size_t)b * p.heads + h) * p.splits;
+  float top = p.sink != nullptr ? p.sink[h] * LOG2E : -FLT_MAX;
+  for (int s = 0; s < p.splits; ++s) top = fmaxf(top, p.part_max[at + s]);
+  float sum = p.sink != nullptr ? fast_exp2(p.sink[h] * LOG2E - top) : 0.f;
+  for (int s = 0; s < p.splits; ++s)
+    if (p.part_max[at + s] != -FLT_MAX) sum += p.part_sum[at + s] * fast_exp2(p.part_max[at + s] - top);
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s)
+      if (p.part_max[at + s] != -FLT_MAX) acc += p.part_out[(at + s) * dv + c] * fast_exp2(p.part_max[at + s] - top);
+    p.out[((size_t)first_token * p.heads + h) * dv + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 template <int D, int DV>
 int launch(const ScoredParams& p, int seqs, int max_q_len, cudaStream_t s) {
   const size_t bytes = (size_t)2 * PREFILL_BKEYS * (D + DV) * 2;
   if (int err = allow_smem(scored_kernel<D, DV>, bytes, "paged_attention_scored_mma")) return err;
-  dim3 grid((max_q_len + PREFILL_BQ - 1) / PREFILL_BQ, p.heads, seqs);
+  const int q_tiles = (max_q_len + PREFILL_BQ - 1) / PREFILL_BQ;
+  dim3 grid(p.splits > 1 ? max(q_tiles, p.splits) : q_tiles, p.heads, seqs);
   launch_kernel(scored_kernel<D, DV>, grid, 128, bytes, s, p);
-  return check_launch("paged_attention_scored_mma");
+  if (int err = check_launch("paged_attention_scored_mma")) return err;
+  if (p.splits > 1) {
+    launch_kernel(scored_merge_kernel, dim3(p.heads, seqs), 64, 0, s, p, DV);
+    return check_launch("paged_attention_scored_merge");
+  }
+  return 0;
 }
 
 bool size_ok(int d) { return d == 32 || d == 64 || d == 128; }
@@ -243,14 +300,17 @@ bool size_ok(int d) { return d == 32 || d == 64 || d == 128; }
 // 1 when the tensor-core kernel takes these head sizes.
 PAE_EXPORT int pae_attention_scored_mma_supports(int d, int dv) { return size_ok(d) && size_ok(dv) ? 1 : 0; }
 
-// bfloat16 only; the arguments of pae_paged_attention_scored without the element type.
+// bfloat16 only; the arguments of pae_paged_attention_scored without the element type. With
+// splits > 1 the keys of every request that brings ONE token are shared out over that many blocks
+// and merged by a second kernel; scratch then holds seqs * heads * splits * (dv + 2) floats.
 PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const void* keys, const void* values,
                                               const int* block_table, int table_width, const int* q_start,
                                               const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads,
                                               int kv_heads, int d, int dv, int page_size, float scale, float cap,
                                               const float* temp, const float* r1, const float* r2, const float* sink,
-                                              int window, int keep_first, void* stream) {
+                                              int window, int keep_first, int splits, float* scratch, void* stream) {
   if (seqs == 0 || max_q_len == 0) return 0;
+  if (splits < 1 || (splits > 1 && scratch == nullptr)) return fail(2, "paged_attention_scored_mma: %d splits", splits);
   if (!pae_attention_scored_mma_supports(d, dv))
     return fail(2, "paged_attention_scored_mma: head sizes %d and %d are not 32, 64 or 128", d, dv);
   if (kv_heads < 1 || heads % kv_heads) return fail(2, "paged_attention_scored_mma: %d heads over %d kv heads", heads, kv_heads);
@@ -262,7 +322,13 @@ PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const vo
     return fail(2, "paged_attention_scored_mma: an operand does not start on a 16-byte boundary");
   ScoredParams p{(__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)keys, (const __nv_bfloat16*)values,
                  block_table, q_start, q_pos0, kv_len, table_width, heads, kv_heads, page_size, window, keep_first,
-                 scale, cap, temp, r1, r2, sink};
+                 scale, cap, temp, r1, r2, sink, splits, nullptr, nullptr, nullptr};
+  if (splits > 1) {
+    const size_t units = (size_t)seqs * heads * splits;
+    p.part_out = scratch;
+    p.part_max = scratch + units * dv;
+    p.part_sum = p.part_max + units;
+  }
   cudaStream_t s = (cudaStream_t)stream;
 #define PAE_SCORED_CASE(DD, DDV) \
   if (d == DD && dv == DDV) return launch<DD, DDV>(p, seqs, max_q_len, s);

@@ -33,7 +33,7 @@ struct DeltaParams {
   const float* w_pre;      // [tokens, heads * d]: w~
   const float* w0;         // [heads * d]
   const float* a_bias;     // [heads * d]
-  float* prepared;         // [tokens, heads, 5 d + 2]: u, w, a u, k, w r, c1, c2
+  float* prepared;         // [tokens, heads, 5 dp + 4]: u, w, a u, k, w r (dp floats each, zero past d), c1, c2, -, -
   float* state;            // [slots, heads, d (value channel), d (key channel)]
   float* o;                // [tokens, heads * d]
   const int* q_start;      // [entries + 1]
@@ -48,6 +48,9 @@ __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x
 __device__ __forceinline__ void copy_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -55,15 +58,17 @@ __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_
 // What the recurrence needs of a token, once per (token, head), by one warp: the decay w, the unit
 // key u, a u, k, w r, and the two sums over key channels that the output needs beside the old
 // state, c1 = sum(a u r) and c2 = sum(k r). Those two are where r meets k head on, so they
-// cancel hardest; they are summed in double and rounded once.
-__global__ void delta_prepare_kernel(DeltaParams p) {
+// cancel hardest; they are summed in double and rounded once. A (token, head) is 5 vectors of
+// `dp` floats (d of them real, the rest zero) and four more floats (c1, c2, two unused): every
+// vector starts on a 16-byte boundary.
+__global__ void delta_prepare_kernel(DeltaParams p, int dp) {
   dependent_launch_prologue();
   const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= p.tokens * p.heads) return;
   const int lane = threadIdx.x & 31;
   const int t = unit / p.heads, h = unit - t * p.heads, d = p.d;
   const float* row = p.proj + (size_t)t * p.ld;
-  float* out = p.prepared + (size_t)unit * (5 * d + 2);
+  float* out = p.prepared + (size_t)unit * (5 * dp + 4);
   float squares = 0.f;
   for (int i = lane; i < d; i += 32) {
     const float k = row[p.k_off + h * d + i];
@@ -71,36 +76,43 @@ __global__ void delta_prepare_kernel(DeltaParams p) {
   }
   const float inv = 1.f / sqrtf(warp_sum(squares) + p.key_eps);
   double c1 = 0.0, c2 = 0.0;
-  for (int i = lane; i < d; i += 32) {
-    const int c = h * d + i;
-    const float k = row[p.k_off + c], r = row[p.r_off + c];
-    const float a = sigmoidf(row[p.a_off + c] + p.a_bias[c]);
-    const float w = expf(-p.decay_scale * sigmoidf(p.w_pre[(size_t)t * p.heads * d + c] + p.w0[c]));
-    const float u = k * inv, au = a * u;
+  for (int i = lane; i < dp; i += 32) {
+    float u = 0.f, w = 0.f, au = 0.f, k = 0.f, wr = 0.f;
+    if (i < d) {
+      const int c = h * d + i;
+      k = row[p.k_off + c];
+      const float r = row[p.r_off + c];
+      const float a = sigmoidf(row[p.a_off + c] + p.a_bias[c]);
+      w = expf(-p.decay_scale * sigmoidf(p.w_pre[(size_t)t * p.heads * d + c] + p.w0[c]));
+      u = k * inv;
+      au = a * u;
+      wr = w * r;
+      c1 += (double)au * (double)r;
+      c2 += (double)k * (double)r;
+    }
     out[i] = u;
-    out[d + i] = w;
-    out[2 * d + i] = au;
-    out[3 * d + i] = k;
-    out[4 * d + i] = w * r;
-    c1 += (double)au * (double)r;
-    c2 += (double)k * (double)r;
+    out[dp + i] = w;
+    out[2 * dp + i] = au;
+    out[3 * dp + i] = k;
+    out[4 * dp + i] = wr;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     c1 += __shfl_xor_sync(0xffffffffu, c1, o);
     c2 += __shfl_xor_sync(0xffffffffu, c2, o);
   }
-  if (lane == 0) {
-    out[5 * d] = (float)c1;
-    out[5 * d + 1] = (float)c2;
-  }
+  if (lane < 4) out[5 * dp + lane] = lane == 0 ? (float)c1 : (lane == 1 ? (float)c2 : 0.f);
 }
 
-// RPT key channels per thread, P threads per value channel (a power of two of at most 32).
+// RPT key channels per thread (a multiple of 4), P threads per value channel (a power of two of at
+// most 32). Thread `part` of a value channel owns the key channels (m P + part) 4 + e for m <
+// RPT / 4, e < 4: its reads of a vector in shared memory are 16 bytes wide, and the P threads of a
+// value channel read P neighbouring 16-byte words (other value channels read the same words), so
+// no two lanes meet in a bank.
 template <int RPT>
 __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) {
   dependent_launch_prologue();
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * p.columns;
   const int d = p.d, dp = P * RPT;
   const int tid = threadIdx.x, threads = blockDim.x;
@@ -109,32 +121,29 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
   const bool owns = column < p.columns && j < d;
   const int first = p.q_start[e], count = p.q_start[e + 1] - first;
 
-  // per tile token: u, w, au, k, wr [dp each], v [columns], c1, c2; two tiles take turns
-  const int per_token = 5 * dp + p.columns + 2;
+  // per tile token: u, w, au, k, wr [dp each], (c1, c2, -, -), v [columns, rounded up to 4]; two tiles take turns
+  const int vectors = 5 * dp + 4;
+  const int per_token = vectors + (p.columns + 3) / 4 * 4;
   const int tile_floats = p.tile * per_token;
-  for (int i = tid; i < 2 * tile_floats; i += threads) smem[i] = 0.f;      // the padding stays zero
   float S[RPT];
   float* mine = p.state + (((size_t)p.state_slot[e] * p.heads + h) * d + (owns ? j : 0)) * d;
 #pragma unroll
   for (int rr = 0; rr < RPT; ++rr) {
-    const int i = part * RPT + rr;
+    const int i = ((rr >> 2) * P + part) * 4 + (rr & 3);
     S[rr] = (owns && i < d) ? mine[i] : 0.f;
   }
-  __syncthreads();
 
-  const int source_floats = 5 * d + 2;
   auto fetch = [&](int t0, float* to) {
     const int n = min(p.tile, count - t0);
-    for (int idx = tid; idx < n * source_floats; idx += threads) {
-      const int tok = idx / source_floats, at = idx - tok * source_floats;
-      const int section = at / d, i = at - section * d;
-      float* dst = to + (size_t)tok * per_token + (section < 5 ? section * dp + i : 5 * dp + p.columns + i);
-      copy_async4(dst, p.prepared + ((size_t)(first + t0 + tok) * p.heads + h) * source_floats + at);
+    const int chunks = vectors / 4;
+    for (int idx = tid; idx < n * chunks; idx += threads) {
+      const int tok = idx / chunks, at = idx - tok * chunks;
+      copy_async16(to + (size_t)tok * per_token + 4 * at, p.prepared + ((size_t)(first + t0 + tok) * p.heads + h) * vectors + 4 * at);
     }
     for (int idx = tid; idx < n * p.columns; idx += threads) {
       const int tok = idx / p.columns, c = idx - tok * p.columns;
       if (j0 + c < d)
-        copy_async4(to + (size_t)tok * per_token + 5 * dp + c, p.proj + (size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c);
+        copy_async4(to + (size_t)tok * per_token + vectors + c, p.proj + (size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c);
     }
   };
 
@@ -151,12 +160,20 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
     // o = S_new^T r written over the old state: sum(w r S_old) - (u^T S_old) c1 + v c2, so that both
     // sums over the state's registers run side by side and share one round of shuffles.
     for (int tok = 0; tok < n; ++tok) {
-      const float* at = tile + (size_t)tok * per_token + part * RPT;
+      const float* at = tile + (size_t)tok * per_token + part * 4;
       float us[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int rr = 0; rr < RPT; ++rr) {
-        us[rr & 3] = fmaf(at[rr], S[rr], us[rr & 3]);
-        rs[rr & 3] = fmaf(at[4 * dp + rr], S[rr], rs[rr & 3]);
+      for (int m = 0; m < RPT / 4; ++m) {
+        const float4 u = *(const float4*)(at + m * P * 4);
+        const float4 wr = *(const float4*)(at + 4 * dp + m * P * 4);
+        us[0] = fmaf(u.x, S[4 * m], us[0]);
+        us[1] = fmaf(u.y, S[4 * m + 1], us[1]);
+        us[2] = fmaf(u.z, S[4 * m + 2], us[2]);
+        us[3] = fmaf(u.w, S[4 * m + 3], us[3]);
+        rs[0] = fmaf(wr.x, S[4 * m], rs[0]);
+        rs[1] = fmaf(wr.y, S[4 * m + 1], rs[1]);
+        rs[2] = fmaf(wr.z, S[4 * m + 2], rs[2]);
+        rs[3] = fmaf(wr.w, S[4 * m + 3], rs[3]);
       }
       float us_all = (us[0] + us[1]) + (us[2] + us[3]), rs_all = (rs[0] + rs[1]) + (rs[2] + rs[3]);
       for (int o = P >> 1; o > 0; o >>= 1) {
@@ -164,11 +181,19 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
         rs_all += __shfl_xor_sync(0xffffffffu, rs_all, o);
       }
       const float* tail = tile + (size_t)tok * per_token + 5 * dp;
-      const float v = owns ? tail[column] : 0.f;
+      const float v = owns ? tail[4 + column] : 0.f;
 #pragma unroll
-      for (int rr = 0; rr < RPT; ++rr) S[rr] = fmaf(at[3 * dp + rr], v, fmaf(-at[2 * dp + rr], us_all, at[dp + rr] * S[rr]));
+      for (int m = 0; m < RPT / 4; ++m) {
+        const float4 w = *(const float4*)(at + dp + m * P * 4);
+        const float4 au = *(const float4*)(at + 2 * dp + m * P * 4);
+        const float4 k = *(const float4*)(at + 3 * dp + m * P * 4);
+        S[4 * m] = fmaf(k.x, v, fmaf(-au.x, us_all, w.x * S[4 * m]));
+        S[4 * m + 1] = fmaf(k.y, v, fmaf(-au.y, us_all, w.y * S[4 * m + 1]));
+        S[4 * m + 2] = fmaf(k.z, v, fmaf(-au.z, us_all, w.z * S[4 * m + 2]));
+        S[4 * m + 3] = fmaf(k.w, v, fmaf(-au.w, us_all, w.w * S[4 * m + 3]));
+      }
       if (owns && part == 0)
-        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[p.columns + 1], fmaf(-us_all, tail[p.columns], rs_all));
+        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[1], fmaf(-us_all, tail[0], rs_all));
     }
     __syncthreads();                              // the tile is read; the fetch after next may refill it
   }
@@ -176,7 +201,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
   if (owns) {
 #pragma unroll
     for (int rr = 0; rr < RPT; ++rr) {
-      const int i = part * RPT + rr;
+      const int i = ((rr >> 2) * P + part) * 4 + (rr & 3);
       if (i < d) mine[i] = S[rr];
     }
   }
@@ -238,9 +263,15 @@ PAE_EXPORT int pae_delta_rule_layout(int d, int* threads_per_column) {
   return 0;
 }
 
+PAE_EXPORT long long pae_delta_rule_scratch_floats(int tokens, int heads, int d) {
+  int P = 0;
+  const int rpt = pae_delta_rule_layout(d, &P);
+  return rpt == 0 ? 0 : (long long)tokens * heads * (5 * P * rpt + 4);
+}
+
 // proj float32 [tokens, ld] holds r, k, v, a~ at the given column offsets (heads * d columns each);
 // w_pre float32 [tokens, heads * d]; state float32 [slots, heads, d, d] (value channel major);
-// o float32 [tokens, heads * d]; prepared float32 scratch of tokens * heads * (5 d + 2).
+// o float32 [tokens, heads * d]; prepared float32 scratch of pae_delta_rule_scratch_floats(...), 16-byte aligned.
 // `column_splits` blocks share a head's value channels.
 PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, const float* proj, int ld, int r_off, int k_off,
                                    int v_off, int a_off, const float* w_pre, const float* w0, const float* a_bias,
@@ -252,6 +283,7 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, cons
   if (rpt == 0) return fail(2, "delta_rule_scan: head size %d is outside [1, 256]", d);
   if (entries > 2147483647 / 2 || heads > 65535) return fail(3, "delta_rule_scan: %d requests x %d heads exceed one launch", entries, heads);
   if (column_splits < 1 || column_splits > d) return fail(2, "delta_rule_scan: %d blocks for %d value channels", column_splits, d);
+  if (((uintptr_t)prepared | (uintptr_t)state) & 15) return fail(2, "delta_rule_scan: the scratch or the state does not start on a 16-byte boundary");
   DeltaParams p{};
   p.proj = proj; p.ld = ld; p.r_off = r_off; p.k_off = k_off; p.v_off = v_off; p.a_off = a_off;
   p.w_pre = w_pre; p.w0 = w0; p.a_bias = a_bias; p.prepared = prepared; p.state = state; p.o = o;
@@ -260,10 +292,10 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, cons
   p.decay_scale = decay_scale; p.key_eps = key_eps;
   cudaStream_t s = (cudaStream_t)stream;
   const long long units = (long long)tokens * heads;
-  launch_kernel(delta_prepare_kernel, (unsigned)((units + 3) / 4), 128, 0, s, p);
-  if (int err = check_launch("delta_rule_prepare")) return err;
   const int dp = P * rpt;
-  const int per_token = 5 * dp + p.columns + 2;
+  launch_kernel(delta_prepare_kernel, (unsigned)((units + 3) / 4), 128, 0, s, p, dp);
+  if (int err = check_launch("delta_rule_prepare")) return err;
+  const int per_token = 5 * dp + 4 + (p.columns + 3) / 4 * 4;
   int tile = 16;
   while (tile > 1 && (size_t)2 * tile * per_token * sizeof(float) > 44 * 1024) tile /= 2;
   p.tile = tile;

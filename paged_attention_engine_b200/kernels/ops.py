@@ -925,13 +925,16 @@ def conv_heads_cache_write(proj, taps_weight, state, positions, seq_index, q_sta
 
 def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
                            value_dim, page_size, max_q_len, scale, softcap=0.0, temp=None, r1=None, r2=None, sink=None,
-                           window: int = 0, keep_first: int = 0, form: str | None = None) -> torch.Tensor:
+                           window: int = 0, keep_first: int = 0, form: str | None = None, max_kv_len: int | None = None,
+                           num_single: int | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages under a score rule:
     (q . k) * scale * temp[h], capped by softcap * tanh(. / softcap), minus r1[h] * log(1 + r2[h] *
     distance), a window that keeps the first `keep_first` keys, and a sink logit per head in the
     softmax's denominator. temp, r1, r2, sink are float32 [heads] or None. -> [tokens, heads * value_dim].
     bfloat16 with head sizes of 32, 64 or 128 runs on tensor cores (csrc/attention_scored_mma.cu), everything
-    else, and everything when `form` is "simt", on the CUDA cores (csrc/attention_scored.cu)."""
+    else, and everything when `form` is "simt", on the CUDA cores (csrc/attention_scored.cu). `max_kv_len` (the
+    longest context of the step) and `num_single` (how many requests bring one token) let the tensor-core
+    kernel share a single token's keys out over several blocks."""
     q = materialized(q)
     _need(q, "paged_attention_scored: q")
     _need(keys, "paged_attention_scored: keys", q.dtype)
@@ -951,10 +954,20 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
             and form != "simt"):
         lib = _lib("attention_scored_mma")
         _set_bounds("attention_scored_mma", keys)
+        # A request that brings one token is one row of one block per head: its keys are shared out
+        # over blocks until the launch fills the GPU about twice (64 keys a tile, at least one tile each).
+        seqs = kv_len.numel()
+        reach = min(max_kv_len, window + keep_first) if window and max_kv_len else (max_kv_len or 0)
+        splits = 1
+        if num_single is None or num_single > 0:
+            splits = max(1, min(-(-reach // 64), (6 * _sm_count(q.device)) // max(1, seqs * num_heads)))
+        scratch = (torch.empty(seqs * num_heads * splits * (value_dim + 2), dtype=torch.float32, device=q.device)
+                   if splits > 1 else None)
         _check(lib, lib.pae_paged_attention_scored_mma(
             _ptr(out), _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start),
             _ptr(q_pos0), _ptr(kv_len), kv_len.numel(), max_q_len, num_heads, num_kv_heads, head_dim, value_dim, page_size,
-            scale, float(softcap or 0.0), _ptr(temp), _ptr(r1), _ptr(r2), _ptr(sink), int(window), int(keep_first), _stream()))
+            scale, float(softcap or 0.0), _ptr(temp), _ptr(r1), _ptr(r2), _ptr(sink), int(window), int(keep_first),
+            splits, _ptr(scratch), _stream()), 2 if splits > 1 else 1)
         return out
     lib = _lib("attention_scored")
     _set_bounds("attention_scored", keys)
@@ -1025,7 +1038,7 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
            and (head_dim // (2 * splits)) * per_column.value >= 128):
         splits *= 2
     o = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
-    prepared = torch.empty(tokens * num_heads * (5 * head_dim + 2), dtype=torch.float32, device=proj.device)
+    prepared = torch.empty(lib.pae_delta_rule_scratch_floats(tokens, num_heads, head_dim), dtype=torch.float32, device=proj.device)
     _check(lib, lib.pae_delta_rule_scan(_ptr(o), _ptr(state), _ptr(prepared), _ptr(proj), ld, offsets[0], offsets[1],
                                         offsets[2], offsets[3], _ptr(w_pre), _ptr(w0), _ptr(a_bias), _ptr(q_start),
                                         _ptr(state_slot), tokens, num_seqs, num_heads, head_dim, splits, decay_scale, key_eps,

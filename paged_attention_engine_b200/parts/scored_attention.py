@@ -99,5 +99,6 @@ class ScoredWindowAttention(Part):
         out = ops.paged_attention_scored(
             q, cache.keys, cache.values, group.block_table, ctx.q_start, ctx.q_pos0, ctx.kv_len, self.num_heads,
             self.num_kv_heads, self.head_dim, self.value_dim, cache.page_size, ctx.max_q_len, self.scale, self.softcap,
-            self.temp, self.r1, self.r2, self.sink, self.window, self.keep_first)
+            self.temp, self.r1, self.r2, self.sink, self.window, self.keep_first, max_kv_len=ctx.max_kv_len,
+            num_single=ctx.num_single)
         return ops.linear(out, self.o_weight, None, residual, out_dtype=residual.dtype)

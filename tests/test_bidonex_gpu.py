@@ -171,7 +171,8 @@ def _attention_case(dtype, T, heads, kv_heads, d, dv, page, rows, size=None, kee
         out = ops.paged_attention_scored(
             q[first : first + count].reshape(count, heads * d).to(DEV).contiguous(), keys, values, block_table,
             _ints([0, count]), _ints([first]), _ints([first + count]), heads, kv_heads, d, dv, page, count, scale, cap or 0.0,
-            dev["temp"], dev["r1"], dev["r2"], dev["sink"], size or 0, keep, form=form)
+            dev["temp"], dev["r1"], dev["r2"], dev["sink"], size or 0, keep, form=form, max_kv_len=first + count,
+            num_single=1 if count == 1 else 0)
         return out.reshape(count, heads, dv)
 
     if decode:
