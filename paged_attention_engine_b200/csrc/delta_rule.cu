@@ -159,8 +159,9 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
     const float* tile = smem + turn * tile_floats;
     // o = S_new^T r written over the old state: sum(w r S_old) - (u^T S_old) c1 + v c2, so that both
     // sums over the state's registers run side by side and share one round of shuffles.
+#pragma unroll 2
     for (int tok = 0; tok < n; ++tok) {
-      const float* at = tile + (size_t)tok * per_token + part * 4;
+      const float* at = tile + tok * per_token + part * 4;
       float us[4] = {0.f, 0.f, 0.f, 0.f}, rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int m = 0; m < RPT / 4; ++m) {
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
         us_all += __shfl_xor_sync(0xffffffffu, us_all, o);
         rs_all += __shfl_xor_sync(0xffffffffu, rs_all, o);
       }
-      const float* tail = tile + (size_t)tok * per_token + 5 * dp;
+      const float* tail = tile + tok * per_token + 5 * dp;
       const float v = owns ? tail[4 + column] : 0.f;
 #pragma unroll
       for (int m = 0; m < RPT / 4; ++m) {
@@ -252,15 +253,21 @@ int pow2_at_least(int n) {
 // per value channel.
 PAE_EXPORT int pae_delta_rule_layout(int d, int* threads_per_column) {
   if (d < 1 || d > 256) return 0;
-  const int choices[4] = {8, 16, 32, 64};
-  for (int rpt : choices) {
-    const int P = pow2_at_least((d + rpt - 1) / rpt);
-    if (P <= 32 && (d * P + 31) / 32 * 32 <= 1024) {
-      if (threads_per_column != nullptr) *threads_per_column = P;
-      return rpt;
-    }
-  }
-  return 0;
+  // Few key channels per thread: a warp's instructions per token are what a block's time is made
+  // of (one token after the other, a handful of warps an SM), and eight channels a thread
+  // with up to 32 threads a value channel keep them fewest. A block then takes at most
+  // 1024 / threads-per-channel value channels: pae_delta_rule_min_splits says how many blocks a head needs.
+  const int P = pow2_at_least((d + 7) / 8);
+  if (threads_per_column != nullptr) *threads_per_column = P;
+  return 8;
+}
+
+// The fewest blocks that a head's value channels must be shared out over (a block has at most 1,024 threads).
+PAE_EXPORT int pae_delta_rule_min_splits(int d) {
+  int P = 0;
+  if (pae_delta_rule_layout(d, &P) == 0) return 0;
+  const int most_columns = 1024 / P;
+  return (d + most_columns - 1) / most_columns;
 }
 
 PAE_EXPORT long long pae_delta_rule_scratch_floats(int tokens, int heads, int d) {
@@ -282,7 +289,8 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, cons
   const int rpt = pae_delta_rule_layout(d, &P);
   if (rpt == 0) return fail(2, "delta_rule_scan: head size %d is outside [1, 256]", d);
   if (entries > 2147483647 / 2 || heads > 65535) return fail(3, "delta_rule_scan: %d requests x %d heads exceed one launch", entries, heads);
-  if (column_splits < 1 || column_splits > d) return fail(2, "delta_rule_scan: %d blocks for %d value channels", column_splits, d);
+  if (column_splits < pae_delta_rule_min_splits(d) || column_splits > d)
+    return fail(2, "delta_rule_scan: %d blocks for %d value channels (at least %d)", column_splits, d, pae_delta_rule_min_splits(d));
   if (((uintptr_t)prepared | (uintptr_t)state) & 15) return fail(2, "delta_rule_scan: the scratch or the state does not start on a 16-byte boundary");
   DeltaParams p{};
   p.proj = proj; p.ld = ld; p.r_off = r_off; p.k_off = k_off; p.v_off = v_off; p.a_off = a_off;
@@ -302,12 +310,7 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, cons
   const size_t bytes = (size_t)2 * tile * per_token * sizeof(float);
   const int threads = (p.columns * P + 31) / 32 * 32;
   dim3 grid(entries, heads, (d + p.columns - 1) / p.columns);
-  switch (rpt) {
-    case 8: launch_kernel(delta_scan_kernel<8>, grid, threads, bytes, s, p, P); break;
-    case 16: launch_kernel(delta_scan_kernel<16>, grid, threads, bytes, s, p, P); break;
-    case 32: launch_kernel(delta_scan_kernel<32>, grid, threads, bytes, s, p, P); break;
-    default: launch_kernel(delta_scan_kernel<64>, grid, threads, bytes, s, p, P); break;
-  }
+  launch_kernel(delta_scan_kernel<8>, grid, threads, bytes, s, p, P);
   return check_launch("delta_rule_scan");
 }
 

@@ -1033,8 +1033,8 @@ def delta_rule(proj, offsets, w_pre, w0, a_bias, gate_offset, norm_weight, state
         raise KernelError(f"delta_rule: head size {head_dim} is not supported (1 to 256)")
     # Few (request, head) pairs leave SMs idle: a head's value channels are shared out over blocks
     # (the recurrence of a value channel needs no other), at least a warp's worth of threads each.
-    splits, sms = 1, _sm_count(proj.device)
-    while (num_seqs * num_heads * splits < sms and head_dim % (2 * splits) == 0
+    splits, sms = lib.pae_delta_rule_min_splits(head_dim), _sm_count(proj.device)
+    while (num_seqs * num_heads * splits < 2 * sms and head_dim % (2 * splits) == 0
            and (head_dim // (2 * splits)) * per_column.value >= 128):
         splits *= 2
     o = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
