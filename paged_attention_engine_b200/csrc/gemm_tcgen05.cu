@@ -50,6 +50,7 @@ struct Params {
   int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
   int out_f32;
   int swiglu;        // NORMAL only: columns come in blocks of 16 gate, 16 up; out[row, n / 2] = silu(gate) * up
+  int activation;    // 0: none; 1: exact GELU, 2: tanh GELU, of the product (+ bias) rounded to the output's type, before the residual
   // q|k|v with rotation and page write in the epilogue (NORMAL, many tokens): out is
   // qkv [tokens, (heads + 2 kv_heads) d]; a tile of 256 columns holds whole heads.
   int rotary;
@@ -77,6 +78,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// The activations a product can apply to its own output. The argument is rounded to the output's
+// element type first, as a stand-alone activation kernel would read it, so both ways give the same bits.
+__device__ __forceinline__ float activation_of(float z, int kind, bool out_f32) {
+  if (!out_f32) z = __bfloat162float(__float2bfloat16_rn(z));
+  if (kind == 1) return 0.5f * z * (1.f + erff(z * 0.70710678118654752440f));
+  return 0.5f * z * (1.f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
 // One thread's 16 consecutive outputs of row `row` from column `col0` on: bias, residual,
 // rounding, store (16-byte stores when the row pitch allows).
 __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, float* v, size_t plane_offset = 0) {
@@ -93,6 +102,10 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int co
         for (int i = 0; i < 16; ++i)
           if (i < valid) v[i] += p.bias[col0 + i];
       }
+    }
+    if (p.activation != 0) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = activation_of(v[i], p.activation, p.out_f32 != 0);
     }
     const size_t at = plane_offset + (size_t)row * p.ld_out + col0;
     if (p.out_f32) {
@@ -808,10 +821,12 @@ PAE_EXPORT int pae_linear_rotary_tcgen05(void* qkv, const void* x, const void* w
 }
 
 PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const float* bias, const void* residual,
-                                  int tokens, int n, int k, int out_f32, int* error, void* stream) {
+                                  int tokens, int n, int k, int out_f32, int activation, int* error, void* stream) {
   if (tokens == 0 || n == 0) return 0;
   if (int err = check_operands(x, w, k)) return err;
+  if (activation < 0 || activation > 2) return fail(2, "linear_tcgen05: activation %d (0: none, 1: exact GELU, 2: tanh GELU)", activation);
   Params p{};
+  p.activation = activation;
   p.out = out;
   p.bias = bias;
   p.residual = residual;
@@ -942,27 +957,28 @@ PAE_EXPORT int pae_sm_count(void) { return sm_count(); }
 // summed in the order of the splits. out and residual bfloat16 or float32.
 template <typename TO>
 __global__ void reduce_splits_kernel(TO* __restrict__ out, const float* __restrict__ partial, const float* __restrict__ bias,
-                                     const TO* __restrict__ residual, int splits, long long plane, int n) {
+                                     const TO* __restrict__ residual, int splits, long long plane, int n, int activation) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= plane) return;
   float v = 0.f;
   for (int s = 0; s < splits; ++s) v += partial[(size_t)s * plane + i];
   if (bias != nullptr) v += bias[i % n];
+  if (activation != 0) v = activation_of(v, activation, sizeof(TO) == 4);
   if (residual != nullptr) v += to_float(residual[i]);
   out[i] = from_float<TO>(v);
 }
 
 PAE_EXPORT int pae_reduce_splits(void* out, const float* partial, const float* bias, const void* residual, int splits,
-                                 int tokens, int n, int out_f32, void* stream) {
+                                 int tokens, int n, int out_f32, int activation, void* stream) {
   const long long plane = (long long)tokens * n;
   if (plane == 0) return 0;
   const unsigned blocks = (unsigned)((plane + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (out_f32)
-    launch_kernel(reduce_splits_kernel<float>, blocks, 256, 0, s, (float*)out, partial, bias, (const float*)residual, splits, plane, n);
+    launch_kernel(reduce_splits_kernel<float>, blocks, 256, 0, s, (float*)out, partial, bias, (const float*)residual, splits, plane, n, activation);
   else
-    launch_kernel(reduce_splits_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, bias, (const __nv_bfloat16*)residual, splits, plane, n);
+    launch_kernel(reduce_splits_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, bias, (const __nv_bfloat16*)residual, splits, plane, n, activation);
   return check_launch("reduce_splits");
 }
 

@@ -164,11 +164,12 @@ class PendingSum:
     included), which saves a launch; anything else calls `materialized`, which runs the
     stand-alone reduction once and keeps its result in `value`."""
 
-    def __init__(self, partial, bias, residual, out_dtype):
+    def __init__(self, partial, bias, residual, out_dtype, activation: int = 0):
         self.partial = partial
         self.bias = bias
         self.residual = residual
         self.dtype = out_dtype
+        self.activation = activation      # applied to sum + bias by the stand-alone reduction only
         self.value = None
 
     @property
@@ -218,7 +219,7 @@ def materialized(x):
         out = torch.empty((m, n), dtype=x.dtype, device=x.partial.device)
         lib = _lib("gemm_tcgen05")
         _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(x.partial), _ptr(x.bias), _ptr(x.residual), splits,
-                                          m, n, (1 if x.dtype == torch.float32 else 0), _stream()))
+                                          m, n, (1 if x.dtype == torch.float32 else 0), x.activation, _stream()))
         x.value = out
     return x.value
 
@@ -267,7 +268,7 @@ def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
     _need(weight, "rms_norm: weight", torch.float32)
     if weight.numel() != x.shape[-1]:
         raise KernelError(f"rms_norm: weight of {weight.numel()} for rows of {x.shape[-1]}")
-    if isinstance(x, PendingSum) and x.value is None:
+    if isinstance(x, PendingSum) and x.value is None and not x.activation:
         splits, m, n = x.partial.shape
         value = torch.empty((m, n), dtype=x.dtype, device=x.device)
         normed = torch.empty_like(value)
@@ -413,9 +414,17 @@ def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
     )
 
 
-def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
-    """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]."""
-    if (bias is None and out_dtype in (None, torch.bfloat16) and weight.dtype == torch.bfloat16 and weight.dim() == 2
+ACTIVATIONS = {None: 0, "gelu_erf": 1, "gelu_tanh": 2}
+
+
+def linear(x, weight, bias=None, residual=None, out_dtype=None, activation: str | None = None) -> torch.Tensor:
+    """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]. `activation`
+    ("gelu_erf", "gelu_tanh") is applied to the product (+ bias), rounded to the output's dtype first,
+    before the residual: in the tensor-core product's epilogue or in the sum of its splits, else
+    by the activation's own kernel."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"linear: activation '{activation}' (known: gelu_erf, gelu_tanh)")
+    if (activation is None and bias is None and out_dtype in (None, torch.bfloat16) and weight.dtype == torch.bfloat16 and weight.dim() == 2
             and weight.data_ptr() % 16 == 0 and weight.shape[0] <= 65536):
         source, norm_weight, eps = _norm_of(x)
         if (_few_tokens(source, weight.shape[1], norm_weight is not None, RESIDUAL_KIND, weight.shape[0]) and source.dim() == 2 and source.shape[1] == weight.shape[1]
@@ -449,7 +458,11 @@ def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     if m == 0:
         return torch.empty((m, n), dtype=out_dtype, device=x.device)
     if _tensor_core_shape(x, weight, residual, out_dtype):
-        return _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k)
+        return _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k, ACTIVATIONS[activation])
+    if activation is not None:
+        if residual is not None:
+            raise KernelError("linear: an activation before a residual needs the tensor-core product")
+        return gelu(linear(x, weight, bias, None, out_dtype), activation)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     lib = _lib("gemm_simt")
     _check(lib, lib.pae_linear_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), m, n,
@@ -458,7 +471,7 @@ def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     return out
 
 
-def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch.Tensor:
+def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k, activation: int = 0) -> torch.Tensor:
     lib = _lib("gemm_tcgen05")
     flag = _error_flag(x.device)
     out_f32 = (1 if out_dtype == torch.float32 else 0)
@@ -469,9 +482,9 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch
         partial = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
         _check(lib, lib.pae_linear_tcgen05_swapped(_ptr(partial), _ptr(x), _ptr(weight), m, n, k,
                                                    _ptr(flag), _stream()))
-        if splits == 1 and bias is None and residual is None and out_dtype == torch.float32:
+        if splits == 1 and bias is None and residual is None and out_dtype == torch.float32 and not activation:
             return partial[0]
-        pending = PendingSum(partial, bias, residual, out_dtype)
+        pending = PendingSum(partial, bias, residual, out_dtype, activation)
         return pending if fuse_split_sums else materialized(pending)
     planes = lib.pae_linear_tcgen05_plane_count(m, n, k)
     if planes > 1:
@@ -480,11 +493,11 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch
         partial = torch.empty((planes, m, n), dtype=torch.float32, device=x.device)
         _check(lib, lib.pae_linear_tcgen05_planes(_ptr(partial), _ptr(x), _ptr(weight), m, n, k,
                                                   planes, _ptr(flag), _stream()))
-        pending = PendingSum(partial, bias, residual, out_dtype)
+        pending = PendingSum(partial, bias, residual, out_dtype, activation)
         return pending if fuse_split_sums else materialized(pending)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), m, n,
-                                       k, out_f32, _ptr(flag), _stream()))
+                                       k, out_f32, activation, _ptr(flag), _stream()))
     return out
 
 
@@ -516,7 +529,7 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         _need(values, "rotary_qk_cache_write: values", qkv.dtype)
     key_ptr = _ptr(keys if slots is not None else None)
     value_ptr = _ptr(values if slots is not None else None)
-    if isinstance(qkv, PendingSum) and qkv.value is None and qkv.residual is None:
+    if isinstance(qkv, PendingSum) and qkv.value is None and qkv.residual is None and not qkv.activation:
         splits = qkv.partial.shape[0]
         out = torch.empty((tokens, width), dtype=qkv.dtype, device=qkv.device)
         lib = _lib("fused_decode")
@@ -733,7 +746,8 @@ def silu_mul(gate_up, block: int = 0) -> torch.Tensor:
     tokens, two_i = gate_up.shape
     if two_i % 2 or (block and two_i % (2 * block)):
         raise KernelError(f"silu_mul: rows of {two_i} do not split into gate and up (blocks of {block})")
-    if isinstance(gate_up, PendingSum) and gate_up.value is None and gate_up.bias is None and gate_up.residual is None:
+    if (isinstance(gate_up, PendingSum) and gate_up.value is None and gate_up.bias is None and gate_up.residual is None
+            and not gate_up.activation):
         splits = gate_up.partial.shape[0]
         out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
         lib = _lib("fused_decode")

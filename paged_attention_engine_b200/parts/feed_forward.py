@@ -70,5 +70,5 @@ class DenseMLP(Part):
 
     def forward(self, ctx, x, residual):
         ops = self.ops
-        hidden = ops.gelu(ops.linear(x, self.up_weight, None), self.activation)
+        hidden = ops.linear(x, self.up_weight, None, activation=self.activation)     # the activation in the product's epilogue
         return ops.linear(hidden, self.down_weight, None, residual, out_dtype=residual.dtype if residual is not None else None)

@@ -63,6 +63,23 @@ def test_gelu_and_embedding_with_positions(dtype):
     assert torch.equal(got.cpu(), table.float()[ids] + pos.float()[places])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m, n, k", [(3, 96, 64), (70, 384, 256), (300, 512, 128), (200, 256, 2048), (130, 100, 72), (40, 90, 30)])
+def test_activation_inside_a_product(dtype, m, n, k):
+    """The activation runs in the product's epilogue, in the sum of its splits or as a kernel of
+    its own, by size; every way is act(x w^T + bias) with the argument rounded to the output's dtype."""
+    ops = _ops()
+    x = torch.randn(m, k).to(dtype)
+    w = (torch.randn(n, k) * 0.3).to(dtype)
+    bias = torch.randn(n)
+    for kind in ("gelu_erf", "gelu_tanh"):
+        z = (x.double() @ w.double().T + bias.double()).to(dtype).double()
+        want = plain.gelu_erf(z) if kind == "gelu_erf" else 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+        got = ops.materialized(ops.linear(x.to(DEV), w.to(DEV), bias.to(DEV), activation=kind))
+        assert got.dtype == dtype
+        _close(got, want, dtype, scale=2.0)
+
+
 def _conv_case(dtype, taps, heads, kv_heads, d, dv, cuts, page, normalize=True, seed=0):
     """Two requests whose projections are cut into portions; returns nothing, asserts."""
     ops = _ops()
