@@ -375,3 +375,35 @@ def test_trace_program_on_a_random_model(folders, tmp_path):
     for key, ids in requests.items():
         want = bh.plain_logits(folders["small_a"], ids)
         assert float((got[key] - want).abs().max()) <= bh.tolerance(torch.bfloat16, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_tolerance_notices_a_window_a_kept_key_or_a_sink_that_is_off(folders, dtype):
+    """The plain model with its window one key longer, one kept key fewer, or without its sinks
+    leaves the tolerance around the engine's logits: the comparisons above could tell."""
+    import copy
+
+    raw, page, seed = bh.SMALL["small_a"]
+    requests = _requests(raw["vocab"], [61], seed)
+    oracle = _oracle(folders["small_a"], requests)
+    got = _check(folders["small_a"], dtype, helpers.trace_whole(requests), requests, oracle, page)["r0"]
+    config, tensors = bh.read_model(folders["small_a"])
+    tol = bh.tolerance(dtype, oracle["r0"])
+
+    def gap(changed_config, changed_tensors):
+        return float((plain.forward(changed_config, changed_tensors, requests["r0"]).float() - got).abs().max())
+
+    longer = copy.deepcopy(config)
+    longer["layers"][1]["mixer"]["mask"]["size"] += 1
+    fewer = copy.deepcopy(config)
+    fewer["layers"][1]["mixer"]["mask"]["keep_first"] -= 1
+    no_sink = dict(tensors)
+    for name in tensors:
+        if name.endswith(".sink"):
+            no_sink[name] = torch.full_like(tensors[name], -40.0)
+    shifted = dict(tensors)
+    shifted["l1.mix.k.conv"] = torch.roll(tensors["l1.mix.k.conv"], 1, dims=1)
+    assert gap(config, tensors) <= tol
+    for what, value in (("window", gap(longer, tensors)), ("kept keys", gap(fewer, tensors)), ("sink", gap(config, no_sink)),
+                        ("taps", gap(config, shifted))):
+        assert value > 1.5 * tol, f"{what}: the plain model with this fault is only {value} away (tolerance {tol})"
