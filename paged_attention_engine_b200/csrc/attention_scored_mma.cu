@@ -34,8 +34,10 @@ struct ScoredParams {
   const float* r1;
   const float* r2;
   const float* sink;
-  // Requests that bring one token can have their keys shared out over `splits` blocks, which leave
-  // unnormalised outputs with their maxima and sums for the merge kernel.
+  // Requests that bring one token (when part_out is given): a block takes one kv head and the
+  // query heads that share it as its rows, so every key is read once per kv head; the keys are
+  // shared out over `splits` such blocks, which leave unnormalised outputs with their maxima and
+  // sums for the merge kernel.
   int splits;
   float* part_out;              // [requests, heads, splits, DV]
   float* part_max;              // [requests, heads, splits]  (in units of log 2)
@@ -55,19 +57,21 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   const int h = blockIdx.y, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
-  const bool shared_out = p.splits > 1 && q_count == 1;
+  const bool shared_out = p.part_out != nullptr && q_count == 1;
   const int tile = shared_out ? 0 : blockIdx.x;
   const int split = shared_out ? blockIdx.x : 0;
-  if (shared_out ? split >= p.splits : tile * PREFILL_BQ >= q_count) return;
+  const int group = p.heads / p.kv_heads;
+  if (shared_out ? (split >= p.splits || h >= p.kv_heads) : tile * PREFILL_BQ >= q_count) return;
   const uint32_t smem_base = smem_u32(smem);
-  const int g = h / (p.heads / p.kv_heads);
+  const int g = shared_out ? h : h / group;          // grouped: blockIdx.y counts kv heads
   const int* table = p.block_table + (size_t)b * p.table_width;
   const int warp_row0 = warp * 16;
   constexpr int K_BYTES = PREFILL_BKEYS * D * 2, V_BYTES = PREFILL_BKEYS * DV * 2, STAGE_BYTES = K_BYTES + V_BYTES;
 
-  const int rows = min(PREFILL_BQ, q_count - tile * PREFILL_BQ);
+  // grouped: the rows are the group's query heads, all at the one token's position
+  const int rows = shared_out ? group : min(PREFILL_BQ, q_count - tile * PREFILL_BQ);
   const int pos0 = p.q_pos0[b] + tile * PREFILL_BQ;
-  const int kv_end = min(p.kv_len[b], pos0 + rows);
+  const int kv_end = shared_out ? min(p.kv_len[b], pos0 + 1) : min(p.kv_len[b], pos0 + rows);
   const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   int kv_begin = (first_key / 16) * 16;
   // Tiles of the kept first keys come first, unless they touch the window's tiles anyway.
@@ -83,7 +87,9 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   uint32_t q[D / 16][4];
   load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
     const int row = warp_row0 + r;
-    return row < rows ? p.q + ((size_t)(first_token + tile * PREFILL_BQ + row) * p.heads + h) * D : nullptr;
+    if (row >= rows) return nullptr;
+    return shared_out ? p.q + ((size_t)first_token * p.heads + g * group + row) * D
+                      : p.q + ((size_t)(first_token + tile * PREFILL_BQ + row) * p.heads + h) * D;
   });
 
   // Rows of a tile that lie at or beyond `limit` are zero-filled and never seen. A thread copies the
@@ -139,13 +145,19 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   const bool has_sink = p.sink != nullptr;
   const float sink2 = has_sink && !shared_out ? p.sink[h] * LOG2E : -FLT_MAX;          // the merge adds it otherwise
   float row_max[2] = {sink2, sink2}, row_sum[2] = {sink2 != -FLT_MAX ? 1.f : 0.f, sink2 != -FLT_MAX ? 1.f : 0.f};
-  const float temp = p.scale * (p.temp != nullptr ? p.temp[h] : 1.f);
+  // The head of each of this lane's two rows: the block's head, or, grouped, the row's own.
+  const int my_row[2] = {warp_row0 + (lane >> 2), warp_row0 + (lane >> 2) + 8};
+  const int my_head[2] = {shared_out ? min(g * group + my_row[0], p.heads - 1) : h,
+                          shared_out ? min(g * group + my_row[1], p.heads - 1) : h};
+  const float temp[2] = {p.scale * (p.temp != nullptr ? p.temp[my_head[0]] : 1.f),
+                         p.scale * (p.temp != nullptr ? p.temp[my_head[1]] : 1.f)};
   const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
   const bool has_bias = p.r1 != nullptr;
-  const float r1 = has_bias ? p.r1[h] : 0.f, r2 = has_bias ? p.r2[h] : 0.f;
-  const int my_pos[2] = {pos0 + warp_row0 + (lane >> 2), pos0 + warp_row0 + (lane >> 2) + 8};
-  const int warp_first_pos = pos0 + warp_row0;
-  const int warp_last_pos = warp_row0 < rows ? pos0 + min(rows, warp_row0 + 16) - 1 : -1;
+  const float r1[2] = {has_bias ? p.r1[my_head[0]] : 0.f, has_bias ? p.r1[my_head[1]] : 0.f};
+  const float r2[2] = {has_bias ? p.r2[my_head[0]] : 0.f, has_bias ? p.r2[my_head[1]] : 0.f};
+  const int my_pos[2] = {shared_out ? pos0 : pos0 + my_row[0], shared_out ? pos0 : pos0 + my_row[1]};
+  const int warp_first_pos = shared_out ? pos0 : pos0 + warp_row0;
+  const int warp_last_pos = warp_row0 < rows ? (shared_out ? pos0 : pos0 + min(rows, warp_row0 + 16) - 1) : -1;
   const int c = (lane & 3) * 2;
 
   int t_begin = 0, t_end = tiles;
@@ -178,9 +190,9 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
           const int half = j >> 1, key = key0 + u * 8 + c + (j & 1);
           const int distance = my_pos[half] - key;
           const bool seen = key < limit && distance >= 0 && (p.window <= 0 || distance < p.window || key < p.keep_first);
-          float x = s[u][j] * temp;
+          float x = s[u][j] * temp[half];
           if (p.cap > 0.f) x = p.cap * fast_tanh(x * inv_cap);
-          if (has_bias && seen) x -= r1 * __logf(1.f + r2 * (float)distance);
+          if (has_bias && seen) x -= r1[half] * __logf(1.f + r2[half] * (float)distance);
           s[u][j] = seen ? x * LOG2E : -FLT_MAX;
           block_max[half] = fmaxf(block_max[half], s[u][j]);
         }
@@ -229,17 +241,19 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
   }
   cp_async_wait<0>();
 
-  if (shared_out) {               // the one row is row 0 of warp 0: lanes 0..3, first half
-    if (warp == 0 && lane < 4) {
-      const size_t at = ((size_t)b * p.heads + h) * p.splits + split;
+  if (shared_out) {               // a row is a query head of the group
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (my_row[half] >= rows) continue;
+      const size_t at = ((size_t)b * p.heads + g * group + my_row[half]) * p.splits + split;
 #pragma unroll
       for (int n = 0; n < DV / 8; ++n) {
-        p.part_out[at * DV + n * 8 + lane * 2] = o[n][0];
-        p.part_out[at * DV + n * 8 + lane * 2 + 1] = o[n][1];
+        p.part_out[at * DV + n * 8 + c] = o[n][half * 2];
+        p.part_out[at * DV + n * 8 + c + 1] = o[n][half * 2 + 1];
       }
-      if (lane == 0) {
-        p.part_max[at] = row_max[0];
-        p.part_sum[at] = row_sum[0];
+      if ((lane & 3) == 0) {
+        p.part_max[at] = row_max[half];
+        p.part_sum[at] = row_sum[half];
       }
     }
     return;
@@ -283,10 +297,10 @@ int launch(const ScoredParams& p, int seqs, int max_q_len, cudaStream_t s) {
   const size_t bytes = (size_t)2 * PREFILL_BKEYS * (D + DV) * 2;
   if (int err = allow_smem(scored_kernel<D, DV>, bytes, "paged_attention_scored_mma")) return err;
   const int q_tiles = (max_q_len + PREFILL_BQ - 1) / PREFILL_BQ;
-  dim3 grid(p.splits > 1 ? max(q_tiles, p.splits) : q_tiles, p.heads, seqs);
+  dim3 grid(p.part_out != nullptr ? max(q_tiles, p.splits) : q_tiles, p.heads, seqs);
   launch_kernel(scored_kernel<D, DV>, grid, 128, bytes, s, p);
   if (int err = check_launch("paged_attention_scored_mma")) return err;
-  if (p.splits > 1) {
+  if (p.part_out != nullptr) {
     launch_kernel(scored_merge_kernel, dim3(p.heads, seqs), 64, 0, s, p, DV);
     return check_launch("paged_attention_scored_merge");
   }
@@ -301,8 +315,9 @@ bool size_ok(int d) { return d == 32 || d == 64 || d == 128; }
 PAE_EXPORT int pae_attention_scored_mma_supports(int d, int dv) { return size_ok(d) && size_ok(dv) ? 1 : 0; }
 
 // bfloat16 only; the arguments of pae_paged_attention_scored without the element type. With
-// splits > 1 the keys of every request that brings ONE token are shared out over that many blocks
-// and merged by a second kernel; scratch then holds seqs * heads * splits * (dv + 2) floats.
+// `scratch` (seqs * heads * splits * (dv + 2) floats) every request that brings ONE token is taken
+// by blocks of one kv head each, whose rows are the query heads that share it, its keys shared out
+// over `splits` blocks and merged by a second kernel; without scratch a single token is a tile of one row.
 PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const void* keys, const void* values,
                                               const int* block_table, int table_width, const int* q_start,
                                               const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads,
@@ -310,7 +325,10 @@ PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const vo
                                               const float* temp, const float* r1, const float* r2, const float* sink,
                                               int window, int keep_first, int splits, float* scratch, void* stream) {
   if (seqs == 0 || max_q_len == 0) return 0;
-  if (splits < 1 || (splits > 1 && scratch == nullptr)) return fail(2, "paged_attention_scored_mma: %d splits", splits);
+  if (splits < 1) return fail(2, "paged_attention_scored_mma: %d splits", splits);
+  if (scratch != nullptr && heads / kv_heads > PREFILL_BQ)
+    return fail(2, "paged_attention_scored_mma: %d query heads per kv head are more than the %d rows of a block", heads / kv_heads, PREFILL_BQ);
+  if (scratch == nullptr && splits != 1) return fail(2, "paged_attention_scored_mma: %d splits without scratch", splits);
   if (!pae_attention_scored_mma_supports(d, dv))
     return fail(2, "paged_attention_scored_mma: head sizes %d and %d are not 32, 64 or 128", d, dv);
   if (kv_heads < 1 || heads % kv_heads) return fail(2, "paged_attention_scored_mma: %d heads over %d kv heads", heads, kv_heads);
@@ -323,7 +341,7 @@ PAE_EXPORT int pae_paged_attention_scored_mma(void* out, const void* q, const vo
   ScoredParams p{(__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)keys, (const __nv_bfloat16*)values,
                  block_table, q_start, q_pos0, kv_len, table_width, heads, kv_heads, page_size, window, keep_first,
                  scale, cap, temp, r1, r2, sink, splits, nullptr, nullptr, nullptr};
-  if (splits > 1) {
+  if (scratch != nullptr) {
     const size_t units = (size_t)seqs * heads * splits;
     p.part_out = scratch;
     p.part_max = scratch + units * dv;
