@@ -109,12 +109,13 @@ __global__ void delta_prepare_kernel(DeltaParams p, int dp) {
 // RPT / 4, e < 4: its reads of a vector in shared memory are 16 bytes wide, and the P threads of a
 // value channel read P neighbouring 16-byte words (other value channels read the same words), so
 // no two lanes meet in a bank.
-template <int RPT>
-__global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) {
+template <int RPT, int P>
+__global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p) {
   dependent_launch_prologue();
   extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * p.columns;
-  const int d = p.d, dp = P * RPT;
+  constexpr int dp = P * RPT;
+  const int d = p.d;
   const int tid = threadIdx.x, threads = blockDim.x;
   const int column = tid / P, part = tid % P;
   const int j = j0 + column;
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
   const int first = p.q_start[e], count = p.q_start[e + 1] - first;
 
   // per tile token: u, w, au, k, wr [dp each], (c1, c2, -, -), v [columns, rounded up to 4]; two tiles take turns
-  const int vectors = 5 * dp + 4;
+  constexpr int vectors = 5 * dp + 4;
   const int per_token = vectors + (p.columns + 3) / 4 * 4;
   const int tile_floats = p.tile * per_token;
   float S[RPT];
@@ -133,17 +134,18 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
     S[rr] = (owns && i < d) ? mine[i] : 0.f;
   }
 
+  // A token's prepared vectors are one run of 16-byte words; its values of this block's channels a few floats.
   auto fetch = [&](int t0, float* to) {
     const int n = min(p.tile, count - t0);
-    const int chunks = vectors / 4;
-    for (int idx = tid; idx < n * chunks; idx += threads) {
-      const int tok = idx / chunks, at = idx - tok * chunks;
-      copy_async16(to + (size_t)tok * per_token + 4 * at, p.prepared + ((size_t)(first + t0 + tok) * p.heads + h) * vectors + 4 * at);
-    }
-    for (int idx = tid; idx < n * p.columns; idx += threads) {
-      const int tok = idx / p.columns, c = idx - tok * p.columns;
-      if (j0 + c < d)
-        copy_async4(to + (size_t)tok * per_token + vectors + c, p.proj + (size_t)(first + t0 + tok) * p.ld + p.v_off + h * d + j0 + c);
+    constexpr int chunks = vectors / 4;
+    const float* from = p.prepared + ((size_t)(first + t0) * p.heads + h) * vectors;
+    const float* values = p.proj + (size_t)(first + t0) * p.ld + p.v_off + h * d + j0;
+    for (int tok = 0; tok < n; ++tok) {
+      for (int at = tid; at < chunks; at += threads) copy_async16(to + 4 * at, from + 4 * at);
+      if (tid < p.columns && j0 + tid < d) copy_async4(to + vectors + tid, values + tid);
+      to += per_token;
+      from += (size_t)p.heads * vectors;
+      values += p.ld;
     }
   };
 
@@ -157,6 +159,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
     copy_async_wait<1>();
     __syncthreads();
     const float* tile = smem + turn * tile_floats;
+    float* o_row = p.o + (size_t)(first + t0) * p.heads * d + h * d + j;
     // o = S_new^T r written over the old state: sum(w r S_old) - (u^T S_old) c1 + v c2, so that both
     // sums over the state's registers run side by side and share one round of shuffles.
 #pragma unroll 2
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
         rs[3] = fmaf(wr.w, S[4 * m + 3], rs[3]);
       }
       float us_all = (us[0] + us[1]) + (us[2] + us[3]), rs_all = (rs[0] + rs[1]) + (rs[2] + rs[3]);
+#pragma unroll
       for (int o = P >> 1; o > 0; o >>= 1) {
         us_all += __shfl_xor_sync(0xffffffffu, us_all, o);
         rs_all += __shfl_xor_sync(0xffffffffu, rs_all, o);
@@ -193,8 +197,8 @@ __global__ void __launch_bounds__(1024) delta_scan_kernel(DeltaParams p, int P) 
         S[4 * m + 2] = fmaf(k.z, v, fmaf(-au.z, us_all, w.z * S[4 * m + 2]));
         S[4 * m + 3] = fmaf(k.w, v, fmaf(-au.w, us_all, w.w * S[4 * m + 3]));
       }
-      if (owns && part == 0)
-        p.o[(size_t)(first + t0 + tok) * p.heads * d + h * d + j] = fmaf(v, tail[1], fmaf(-us_all, tail[0], rs_all));
+      if (owns && part == 0) *o_row = fmaf(v, tail[1], fmaf(-us_all, tail[0], rs_all));
+      o_row += p.heads * d;
     }
     __syncthreads();                              // the tile is read; the fetch after next may refill it
   }
@@ -310,7 +314,14 @@ PAE_EXPORT int pae_delta_rule_scan(float* o, float* state, float* prepared, cons
   const size_t bytes = (size_t)2 * tile * per_token * sizeof(float);
   const int threads = (p.columns * P + 31) / 32 * 32;
   dim3 grid(entries, heads, (d + p.columns - 1) / p.columns);
-  launch_kernel(delta_scan_kernel<8>, grid, threads, bytes, s, p, P);
+  switch (P) {
+    case 1: launch_kernel(delta_scan_kernel<8, 1>, grid, threads, bytes, s, p); break;
+    case 2: launch_kernel(delta_scan_kernel<8, 2>, grid, threads, bytes, s, p); break;
+    case 4: launch_kernel(delta_scan_kernel<8, 4>, grid, threads, bytes, s, p); break;
+    case 8: launch_kernel(delta_scan_kernel<8, 8>, grid, threads, bytes, s, p); break;
+    case 16: launch_kernel(delta_scan_kernel<8, 16>, grid, threads, bytes, s, p); break;
+    default: launch_kernel(delta_scan_kernel<8, 32>, grid, threads, bytes, s, p); break;
+  }
   return check_launch("delta_rule_scan");
 }
 
