@@ -145,6 +145,7 @@ def test_short_convolution_across_portions(dtype):
     _conv_case(dtype, 2, 2, 1, 96, 96, [[33, 2], [1, 40]], 16, seed=2)
     _conv_case(dtype, 1, 2, 2, 8, 8, [[6, 3], [4]], 4, seed=3)          # one tap: a scale per channel, no state
     _conv_case(dtype, 0, 2, 1, 40, 8, [[6, 3], [4]], 4, normalize=False, seed=4)
+    _conv_case(dtype, 6, 1, 1, 33, 65, [[2, 2, 2, 9, 1], [3, 11]], 4, seed=5)     # more taps than the unrolled kernels take
 
 
 def _attention_case(dtype, T, heads, kv_heads, d, dv, page, rows, size=None, keep=0, cap=None, bias=True, sink=True,

@@ -125,3 +125,14 @@ def test_plain_mechanisms_on_known_values():
     v = torch.tensor([[[4.0, 8.0]]], dtype=torch.float64)
     assert plain.scored_attention(q, q, v, 1.0)[0, 0].tolist() == [4.0, 8.0]
     assert plain.scored_attention(q, q, v, 1.0, sink=torch.zeros(1))[0, 0].tolist() == [2.0, 4.0]
+
+
+def test_command_line_writes_a_random_model(tmp_path):
+    from paged_attention_engine_b200 import cli
+
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(bh.SMALL_B))
+    assert cli.main(["random-model", "--config", str(config), "--seed", "3", "--dtype", "bfloat16", "--out", str(tmp_path / "m")]) == 0
+    raw, tensors = bh.read_model(tmp_path / "m")
+    assert BidonexConfig.from_dict(raw) == BidonexConfig.from_dict(bh.SMALL_B)
+    assert tensors["l1.mix.w1"].shape == (16, 96) and tensors["pos"].shape == (512, 96)
