@@ -60,6 +60,30 @@ def replays() -> None:
         print(f"replayed hidden {raw['hidden_size']} under the checked build: no index out of range", flush=True)
 
 
+def bidonex_replays() -> None:
+    """The second architecture under the checked build: windows with kept first keys whose other
+    pages have been given back, on the tensor-core and the CUDA-core attention."""
+    import bidonex_helpers as bh
+
+    for name in ("small_c", "small_b"):
+        raw, page, seed = bh.SMALL[name]
+        for dtype_name, dtype in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+            with tempfile.TemporaryDirectory() as tmp:
+                folder = bh.write_model(Path(tmp) / "m", raw, seed)
+                requests = {f"r{i}": helpers.random_tokens(raw["vocab"], n, seed + i) for i, n in enumerate((61, 9, 38, 2, 47, 23))}
+                trace = helpers.trace_mixed(requests, seed=21 + seed, live_limit=3)
+                trace = helpers.trace_whole({"r0": requests["r0"]}, first_step=10_000) + trace
+                outputs, replayer = helpers.run_in_process(folder, dtype_name, trace, helpers.max_live_tokens(trace), page)
+                assert not replayer.runner.use_graphs
+                ops.check_device_errors()
+                got = helpers.collect(trace[1:], outputs, requests)
+                for key, ids in requests.items():
+                    want = bh.plain_logits(folder, ids)
+                    gap = (got[key] - want).abs().max().item()
+                    assert gap <= bh.tolerance(dtype, want), f"{name}/{dtype_name}/{key}: {gap}"
+        print(f"replayed {name} under the checked build: no index out of range", flush=True)
+
+
 def caught(code: int) -> None:
     try:
         ops.check_device_errors()
@@ -111,4 +135,5 @@ if __name__ == "__main__":
     assert build.BOUNDS and ops.bounds_checked, "run with PAE_BOUNDS=1"
     violations()
     replays()
+    bidonex_replays()
     print("BOUNDS PROBE OK")
