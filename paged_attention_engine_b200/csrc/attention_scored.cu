@@ -10,7 +10,11 @@
 // Every part of the rule is optional (a null pointer or a zero turns it off), so the kernel also
 // computes plain causal or windowed attention. Value heads may have another size (dv) than query
 // and key heads (d); queries come as their own [tokens, heads, d] tensor. Any d and dv up to 256.
-// Scores, the rule's arithmetic and the running softmax are float32 for both element types.
+// Scores, the rule's arithmetic and the running softmax are float32 for bfloat16 tensors. For
+// float32 tensors they are double: a score that is a sum of d float32 products, sharpened by a
+// temperature and exponentiated, carries several units of float32 rounding into its weight when
+// it is summed in float32, and layers that cancel downstream multiply that; summed and
+// transformed in double, a weight is as good as its float32 inputs allow.
 //
 // A block owns 16 consecutive query tokens of one request and one query head and walks that
 // request's pages in place, 32 keys at a time, over two ranges: the kept first keys and the
@@ -41,7 +45,15 @@ struct ScoreRule {
   int keep_first;        // keys below this position stay visible under a window
 };
 
-template <typename T>
+__device__ __forceinline__ float exp_of(float x) { return expf(x); }
+__device__ __forceinline__ double exp_of(double x) { return exp(x); }
+__device__ __forceinline__ float tanh_of(float x) { return tanhf(x); }
+__device__ __forceinline__ double tanh_of(double x) { return tanh(x); }
+__device__ __forceinline__ float log1p_of(float x) { return log1pf(x); }
+__device__ __forceinline__ double log1p_of(double x) { return log1p(x); }
+
+// A: the type of scores, weights and sums (float for bfloat16 tensors, double for float32 ones).
+template <typename T, typename A>
 __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ keys, const T* __restrict__ values,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ q_start,
@@ -75,15 +87,17 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
     qs[row * dpad + k] = row < rows ? to_float(q[((size_t)(first_token + tile * BQ + row) * heads + h) * d + k]) : 0.f;
   }
 
-  const float temp = rule.scale * (rule.temp != nullptr ? rule.temp[h] : 1.f);
-  const float r1 = rule.r1 != nullptr ? rule.r1[h] : 0.f;
-  const float r2 = rule.r1 != nullptr ? rule.r2[h] : 0.f;
-  float acc[MAX_D / 8];
+  const A lowest = (A)-FLT_MAX;
+  const A temp = (A)rule.scale * (rule.temp != nullptr ? (A)rule.temp[h] : (A)1);
+  const A cap = (A)rule.cap;
+  const A r1 = rule.r1 != nullptr ? (A)rule.r1[h] : (A)0;
+  const A r2 = rule.r1 != nullptr ? (A)rule.r2[h] : (A)0;
+  A acc[MAX_D / 8];
 #pragma unroll
-  for (int i = 0; i < MAX_D / 8; ++i) acc[i] = 0.f;
+  for (int i = 0; i < MAX_D / 8; ++i) acc[i] = (A)0;
   // The sink is a logit that is always there: the running maximum starts at it, the sum at exp(0).
-  float row_max = rule.sink != nullptr ? rule.sink[h] : -FLT_MAX;
-  float row_sum = rule.sink != nullptr ? 1.f : 0.f;
+  A row_max = rule.sink != nullptr ? (A)rule.sink[h] : lowest;
+  A row_sum = rule.sink != nullptr ? (A)1 : (A)0;
   const int my_pos = p0 + r;
   const int nd = (dv + 7) >> 3;
   const int* table = block_table + (size_t)b * table_width;
@@ -107,32 +121,35 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
       }
       __syncthreads();
 
-      float s[BKEYS / 8];
-      float tile_max = -FLT_MAX;
+      A s[BKEYS / 8];
+      A tile_max = lowest;
 #pragma unroll
       for (int i = 0; i < BKEYS / 8; ++i) {
         const int c = cg + 8 * i;
         const int j = base + c;
-        float dot = 0.f;
-        for (int k = 0; k < d; ++k) dot = fmaf(qs[r * dpad + k], ks[c * dpad + k], dot);
+        A dot = (A)0;
+        for (int k = 0; k < d; ++k) dot = fma((A)qs[r * dpad + k], (A)ks[c * dpad + k], dot);
         const int distance = my_pos - j;
         const bool seen = r < rows && j < end && distance >= 0 &&
                           (rule.window <= 0 || distance < rule.window || j < rule.keep_first);
-        float score = dot * temp;
-        if (rule.cap > 0.f) score = rule.cap * tanhf(score / rule.cap);
-        if (rule.r1 != nullptr && seen) score -= r1 * log1pf(r2 * (float)distance);
-        s[i] = seen ? score : -FLT_MAX;
-        tile_max = fmaxf(tile_max, s[i]);
+        A score = dot * temp;
+        if (rule.cap > 0.f) score = cap * tanh_of(score / cap);
+        if (rule.r1 != nullptr && seen) score -= r1 * log1p_of(r2 * (A)distance);
+        s[i] = seen ? score : lowest;
+        tile_max = s[i] > tile_max ? s[i] : tile_max;
       }
 #pragma unroll
-      for (int o = 4; o > 0; o >>= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
-      const float new_max = fmaxf(row_max, tile_max);
-      const float rescale = (row_max == -FLT_MAX) ? 0.f : expf(row_max - new_max);
-      float tile_sum = 0.f;
+      for (int o = 4; o > 0; o >>= 1) {
+        const A other = __shfl_xor_sync(0xffffffffu, tile_max, o);
+        tile_max = other > tile_max ? other : tile_max;
+      }
+      const A new_max = row_max > tile_max ? row_max : tile_max;
+      const A rescale = (row_max == lowest) ? (A)0 : exp_of(row_max - new_max);
+      A tile_sum = (A)0;
 #pragma unroll
       for (int i = 0; i < BKEYS / 8; ++i) {
-        const float p = (s[i] == -FLT_MAX) ? 0.f : expf(s[i] - new_max);
-        ps[r * (BKEYS + 1) + cg + 8 * i] = p;
+        const A p = (s[i] == lowest) ? (A)0 : exp_of(s[i] - new_max);
+        ps[r * (BKEYS + 1) + cg + 8 * i] = (float)p;
         tile_sum += p;
       }
 #pragma unroll
@@ -143,10 +160,10 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
 #pragma unroll
       for (int i = 0; i < MAX_D / 8; ++i) {
         if (i < nd) {
-          float v = acc[i] * rescale;
+          A v = acc[i] * rescale;
           const int dim = cg + 8 * i;
           if (dim < dv)
-            for (int c = 0; c < BKEYS; ++c) v = fmaf(ps[r * (BKEYS + 1) + c], vs[c * dv + dim], v);
+            for (int c = 0; c < BKEYS; ++c) v = fma((A)ps[r * (BKEYS + 1) + c], (A)vs[c * dv + dim], v);
           acc[i] = v;
         }
       }
@@ -154,11 +171,11 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
   }
 
   if (r < rows) {
-    const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+    const A inv = row_sum > (A)0 ? (A)1 / row_sum : (A)0;
     T* to = out + ((size_t)(first_token + tile * BQ + r) * heads + h) * dv;
 #pragma unroll
     for (int i = 0; i < MAX_D / 8; ++i)
-      if (i < nd && cg + 8 * i < dv) to[cg + 8 * i] = from_float<T>(acc[i] * inv);
+      if (i < nd && cg + 8 * i < dv) to[cg + 8 * i] = from_float<T>((float)(acc[i] * inv));
   }
 }
 
@@ -166,12 +183,12 @@ size_t smem_bytes(int d, int dv) {
   return sizeof(float) * (size_t)(BQ * (d + 1) + BKEYS * (d + 1) + BKEYS * dv + BQ * (BKEYS + 1));
 }
 
-template <typename T>
+template <typename T, typename A>
 int launch(void* out, const void* q, const void* keys, const void* values, const int* block_table, int table_width,
            const int* q_start, const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads, int kv_heads,
            int d, int dv, int page_size, const ScoreRule& rule, cudaStream_t s) {
   const size_t bytes = smem_bytes(d, dv);
-  auto kernel = attention_scored_kernel<T>;
+  auto kernel = attention_scored_kernel<T, A>;
   static bool raised = false;
   if (bytes > 48 * 1024 && !raised) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(MAX_D, MAX_D));
@@ -205,10 +222,10 @@ PAE_EXPORT int pae_paged_attention_scored(void* out, const void* q, const void* 
   ScoreRule rule{scale, cap, temp, r1, r2, sink, window, keep_first};
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    return launch<float>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len, heads,
+    return launch<float, double>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len, heads,
                          kv_heads, d, dv, page_size, rule, s);
   if (dtype == kBF16)
-    return launch<__nv_bfloat16>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len,
+    return launch<__nv_bfloat16, float>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len,
                                  heads, kv_heads, d, dv, page_size, rule, s);
   return fail(1, "paged_attention_scored: unknown dtype %d", dtype);
 }
