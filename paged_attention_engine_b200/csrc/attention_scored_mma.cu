@@ -274,20 +274,35 @@ __global__ void __launch_bounds__(128) scored_kernel(const ScoredParams p) {
 // order, with the sink's logit in the denominator.
 __global__ void scored_merge_kernel(const ScoredParams p, int dv) {
   dependent_launch_prologue();
+  extern __shared__ float weights[];          // [splits]: what a block's partial result counts for
+  __shared__ float stats[2];
   const int h = blockIdx.x, b = blockIdx.y;
   const int first_token = p.q_start[b];
   if (p.q_start[b + 1] - first_token != 1) return;
   const size_t at = ((size_t)b * p.heads + h) * p.splits;
-  float top = p.sink != nullptr ? p.sink[h] * LOG2E : -FLT_MAX;
-  for (int s = 0; s < p.splits; ++s) top = fmaxf(top, p.part_max[at + s]);
-  float sum = p.sink != nullptr ? fast_exp2(p.sink[h] * LOG2E - top) : 0.f;
-  for (int s = 0; s < p.splits; ++s)
-    if (p.part_max[at + s] != -FLT_MAX) sum += p.part_sum[at + s] * fast_exp2(p.part_max[at + s] - top);
-  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {                      // one warp: the maximum, then every block's weight and the sum, in the blocks' order
+    const float sink2 = p.sink != nullptr ? p.sink[h] * LOG2E : -FLT_MAX;
+    float top = sink2;
+    for (int s = lane; s < p.splits; s += 32) top = fmaxf(top, p.part_max[at + s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    for (int s = lane; s < p.splits; s += 32) {
+      const float m = p.part_max[at + s];
+      weights[s] = m == -FLT_MAX ? 0.f : fast_exp2(m - top);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      float sum = sink2 != -FLT_MAX ? fast_exp2(sink2 - top) : 0.f;
+      for (int s = 0; s < p.splits; ++s) sum += p.part_sum[at + s] * weights[s];
+      stats[0] = sum > 0.f ? 1.f / sum : 0.f;
+    }
+  }
+  __syncthreads();
+  const float inv = stats[0];
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < p.splits; ++s)
-      if (p.part_max[at + s] != -FLT_MAX) acc += p.part_out[(at + s) * dv + c] * fast_exp2(p.part_max[at + s] - top);
+    for (int s = 0; s < p.splits; ++s) acc += p.part_out[(at + s) * dv + c] * weights[s];
     p.out[((size_t)first_token * p.heads + h) * dv + c] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -301,7 +316,7 @@ int launch(const ScoredParams& p, int seqs, int max_q_len, cudaStream_t s) {
   launch_kernel(scored_kernel<D, DV>, grid, 128, bytes, s, p);
   if (int err = check_launch("paged_attention_scored_mma")) return err;
   if (p.part_out != nullptr) {
-    launch_kernel(scored_merge_kernel, dim3(p.heads, seqs), 64, 0, s, p, DV);
+    launch_kernel(scored_merge_kernel, dim3(p.heads, seqs), 64, (size_t)p.splits * sizeof(float), s, p, DV);
     return check_launch("paged_attention_scored_merge");
   }
   return 0;
