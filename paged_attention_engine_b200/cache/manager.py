@@ -36,10 +36,16 @@ class KVGroupSpec:
     entries: tuple[int, ...]       # schedule positions that own keys and values here
     value_dim: int = 0             # 0: values have the keys' head size
     keep_first: int = 0            # with a window: the first keys stay visible, their pages are never given back
+    values_in_keys: bool = False   # the values are the keys' leading channels: the pages hold keys only
 
     @property
     def value_head_dim(self) -> int:
         return self.value_dim or self.head_dim
+
+    @property
+    def stored_per_token(self) -> int:
+        """Elements that one token adds to one entry of the group."""
+        return self.num_kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_head_dim))
 
 
 @dataclass(frozen=True)
@@ -52,8 +58,7 @@ class CachePlan:
     def bytes_per_block(self, block_size: int, element_size: int) -> int:
         """Bytes of one page id: its keys and values in every entry of every group (each group
         has a pool of its own with the same number of pages)."""
-        return sum(len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * block_size * element_size
-                   for g in self.groups)
+        return sum(len(g.entries) * g.stored_per_token * block_size * element_size for g in self.groups)
 
 
 def layer_needs(layer) -> tuple[CacheNeed | None, StateNeed | None]:
@@ -92,7 +97,8 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
         if entry.cache_from is None and need is not None:
             by_need.setdefault(need, []).append(pos)
     groups = tuple(
-        KVGroupSpec(need.num_kv_heads, need.head_dim, need.window, tuple(entries), need.value_dim, need.keep_first)
+        KVGroupSpec(need.num_kv_heads, need.head_dim, need.window, tuple(entries), need.value_dim, need.keep_first,
+                    need.values_in_keys)
         for need, entries in by_need.items()
     )
     entry_group: dict[int, tuple[int, int]] = {}
@@ -104,8 +110,8 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
     for pos, entry in enumerate(spec.schedule):
         if entry.cache_from is not None and needs[pos] is not None:
             src = needs[entry.cache_from]
-            if src is None or (src.num_kv_heads, src.head_dim, src.value_dim) != (
-                    needs[pos].num_kv_heads, needs[pos].head_dim, needs[pos].value_dim):
+            if src is None or (src.num_kv_heads, src.head_dim, src.value_dim, src.values_in_keys) != (
+                    needs[pos].num_kv_heads, needs[pos].head_dim, needs[pos].value_dim, needs[pos].values_in_keys):
                 raise ValueError(
                     f"schedule[{pos}] reads the cache of entry {entry.cache_from}, whose keys have another shape"
                 )

@@ -23,12 +23,17 @@ class PagedKVCache:
         self.device = torch.device(device)
         self.page_size = manager.block_size
         # A group whose values have the keys' head size is one tensor (keys at index 0, values at 1);
-        # with another value size the values are a tensor of their own and `pools[g]` holds the keys.
+        # with another value size the values are a tensor of their own and `pools[g]` holds the keys;
+        # a group whose values are the leading channels of its keys has the keys' tensor only.
         self.pools: list[torch.Tensor] = []
         self.value_pools: list[torch.Tensor | None] = []
         for group, allocator in zip(plan.groups, manager.allocators):
             n, pages = len(group.entries), allocator.num_blocks
-            if group.value_head_dim == group.head_dim:
+            if group.values_in_keys:
+                self.pools.append(torch.zeros((n, 1, pages, group.num_kv_heads, self.page_size, group.head_dim),
+                                              dtype=dtype, device=self.device))
+                self.value_pools.append(None)
+            elif group.value_head_dim == group.head_dim:
                 shape = (n, 2, pages, group.num_kv_heads, self.page_size, group.head_dim)
                 self.pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
                 self.value_pools.append(None)
@@ -50,7 +55,10 @@ class PagedKVCache:
             g, i = self.plan.entry_group[position]
             view.group = g
             view.keys = self.pools[g][i, 0]
-            view.values = self.pools[g][i, 1] if self.value_pools[g] is None else self.value_pools[g][i]
+            if self.plan.groups[g].values_in_keys:
+                view.values = view.keys
+            else:
+                view.values = self.pools[g][i, 1] if self.value_pools[g] is None else self.value_pools[g][i]
             view.writes = self.plan.entry_writes[position]
         return view
 
@@ -67,4 +75,4 @@ class PagedKVCache:
     def bytes_per_token(self) -> int:
         """Key and value bytes that one token adds over all entries of all groups."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * size for g in self.plan.groups)
+        return sum(len(g.entries) * g.stored_per_token * size for g in self.plan.groups)

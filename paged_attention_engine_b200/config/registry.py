@@ -18,6 +18,7 @@ from .errors import ConfigError
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .bidonex import BidonexConfig
 from .qwen2 import Qwen2Config
+from .zugarax import ZugaraxConfig
 
 
 @dataclass(frozen=True)
@@ -186,3 +187,88 @@ def bidonex_spec(cfg: BidonexConfig) -> ModelSpec:
 
 
 register_architecture("Bidonex", BidonexConfig, bidonex_spec)
+
+
+# --------------------------------------------------------------------------- #
+# Zugarax: a scaled token embedding into a float32 residual stream; pre-norm layers (RMS norm,
+# mixer, add; RMS norm, feed-forward, add; a layer may have no feed-forward); three mixers: a
+# gated sliding-window attention with normed, partly rotated heads and one added to the softmax's
+# denominator, a latent attention whose cache holds one normed latent and one rotated key part per
+# token (a layer may read an earlier layer's), and the matrix memory of xLSTM; a feed-forward
+# whose gate and up projections are clamped; RMS norm, an untied head and a tanh cap on the logits.
+# --------------------------------------------------------------------------- #
+
+# Fixed by the design: the gate's sigmoid is sharpened by 1.702; the sink's logit is 0.
+ZUGARAX_GLU_ALPHA = 1.702
+# The design has no longest sequence; positions are 32-bit integers.
+ZUGARAX_MAX_POSITIONS = 1 << 30
+
+
+def zugarax_spec(cfg: ZugaraxConfig) -> ModelSpec:
+    layers = []
+    schedule = []
+    for i, layer in enumerate(cfg.layers):
+        prefix = f"l{i}"
+        m = layer.mixer
+        cache_from = None
+        if layer.type == "attention":
+            scaling = dict(m.rot.scaling, kind="banded") if m.rot.scaling is not None else None
+            mixer = PartSpec(
+                "gated_window_attention",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
+                    "value_dim": m.vdim, "scale": m.scale, "window": m.window, "qk_norm_eps": cfg.norm_eps,
+                    "unit_sink": True, "output_gate": True,
+                    "position_encoding": {"kind": "scaled_rotary", "dims": m.rot.dims, "base": m.rot.base, "scaling": scaling},
+                },
+                f"{prefix}.mix",
+            )
+        elif layer.type == "latent_attention":
+            scaling = dict(m.rot.scaling, kind="ramped") if m.rot.scaling is not None else None
+            mixer = PartSpec(
+                "latent_attention",
+                {
+                    "hidden_size": cfg.width, "num_heads": m.heads, "head_dim": m.dim, "rot_dim": m.rot_dim,
+                    "value_dim": m.vdim, "kv_rank": m.kv_rank, "scale": m.scale, "norm_eps": cfg.norm_eps,
+                    "own_latent": m.kv_from is None,
+                    "position_encoding": {"kind": "scaled_rotary", "dims": m.rot.dims, "base": m.rot.base, "scaling": scaling},
+                },
+                f"{prefix}.mix",
+            )
+            cache_from = m.kv_from
+        else:
+            mixer = PartSpec(
+                "matrix_memory",
+                {"hidden_size": cfg.width, "num_heads": m.heads, "head_dim": m.dim, "value_dim": m.vdim,
+                 "gate_cap": m.gate_cap, "norm_eps": cfg.norm_eps},
+                f"{prefix}.mix",
+            )
+        norm = lambda name: PartSpec("rms_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine"},
+                                     names={"weight": f"{prefix}.{name}"})
+        if layer.ff:
+            parts = dict(
+                mixer_norm=norm("norm1"), mixer=mixer, feed_forward_norm=norm("norm2"),
+                feed_forward=PartSpec(
+                    "clamped_glu", {"hidden_size": cfg.width, "intermediate_size": layer.ff, "limit": layer.limit,
+                                    "alpha": ZUGARAX_GLU_ALPHA},
+                    f"{prefix}.mlp"))
+            layers.append(LayerSpec("pre_norm_residual", parts))
+        else:
+            layers.append(LayerSpec("mixer_residual", dict(norm=norm("norm1"), mixer=mixer)))
+        schedule.append(ScheduleEntry(i, cache_from))
+    return ModelSpec(
+        architecture=cfg.architecture,
+        vocab_size=cfg.vocab,
+        hidden_size=cfg.width,
+        max_positions=ZUGARAX_MAX_POSITIONS,
+        embedding=PartSpec("scaled_token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "scale": cfg.embedding_scale},
+                           names={"weight": "embed"}),
+        layers=tuple(layers),
+        schedule=tuple(schedule),
+        final_norm=PartSpec("rms_norm", {"size": cfg.width, "eps": cfg.norm_eps, "out": "engine"}, names={"weight": "final.norm"}),
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied_to": None, "softcap": cfg.logit_softcap},
+                      names={"weight": "head"}),
+    )
+
+
+register_architecture("Zugarax", ZugaraxConfig, zugarax_spec)

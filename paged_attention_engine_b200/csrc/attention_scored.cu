@@ -9,7 +9,8 @@
 //
 // Every part of the rule is optional (a null pointer or a zero turns it off), so the kernel also
 // computes plain causal or windowed attention. Value heads may have another size (dv) than query
-// and key heads (d); queries come as their own [tokens, heads, d] tensor. Any d and dv up to 256.
+// and key heads (d); queries come as their own [tokens, heads, d] tensor. Any d that fits shared
+// memory, dv up to 512; the values may be the leading channels of the keys themselves.
 // Scores, the rule's arithmetic and the running softmax are float32 for bfloat16 tensors. For
 // float32 tensors they are double: a score that is a sum of d float32 products, sharpened by a
 // temperature and exponentiated, carries several units of float32 rounding into its weight when
@@ -32,7 +33,6 @@ namespace {
 constexpr int BQ = 16;
 constexpr int BKEYS = 32;
 constexpr int THREADS = 128;
-constexpr int MAX_D = 256;
 
 struct ScoreRule {
   float scale;
@@ -53,12 +53,15 @@ __device__ __forceinline__ float log1p_of(float x) { return log1pf(x); }
 __device__ __forceinline__ double log1p_of(double x) { return log1p(x); }
 
 // A: the type of scores, weights and sums (float for bfloat16 tensors, double for float32 ones).
-template <typename T, typename A>
+// MAX_D: the most value channels (a thread keeps MAX_D / 8 of them). `vs_row` is the distance
+// between two value rows in elements: dv for a value tensor of its own, the key rows' d when
+// the values are the leading channels of the keys themselves (values == keys).
+template <typename T, typename A, int MAX_D>
 __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ keys, const T* __restrict__ values,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ q_start,
     const int* __restrict__ q_pos0, const int* __restrict__ kv_len, int heads, int kv_heads, int d, int dv,
-    int page_size, ScoreRule rule) {
+    int vs_row, int page_size, ScoreRule rule) {
   dependent_launch_prologue();
   extern __shared__ float smem[];
   const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
           const int page = checked_page(table[checked_table_index(j / page_size, table_width)]);
           const size_t row = ((size_t)page * kv_heads + g) * page_size + (j % page_size);
           for (int k = lane; k < d; k += 32) ks[c * dpad + k] = to_float(keys[row * d + k]);
-          for (int k = lane; k < dv; k += 32) vs[c * dv + k] = to_float(values[row * dv + k]);
+          for (int k = lane; k < dv; k += 32) vs[c * dv + k] = to_float(values[row * vs_row + k]);
         } else {
           for (int k = lane; k < d; k += 32) ks[c * dpad + k] = 0.f;
           for (int k = lane; k < dv; k += 32) vs[c * dv + k] = 0.f;
@@ -179,32 +182,49 @@ __global__ void __launch_bounds__(THREADS) attention_scored_kernel(
   }
 }
 
+constexpr size_t SMEM_LIMIT = 200 * 1024;
+constexpr int MOST_CHANNELS = 512;
+
 size_t smem_bytes(int d, int dv) {
   return sizeof(float) * (size_t)(BQ * (d + 1) + BKEYS * (d + 1) + BKEYS * dv + BQ * (BKEYS + 1));
 }
 
-template <typename T, typename A>
-int launch(void* out, const void* q, const void* keys, const void* values, const int* block_table, int table_width,
-           const int* q_start, const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads, int kv_heads,
-           int d, int dv, int page_size, const ScoreRule& rule, cudaStream_t s) {
+template <typename T, typename A, int MAX_D>
+int launch_sized(void* out, const void* q, const void* keys, const void* values, const int* block_table, int table_width,
+                 const int* q_start, const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads, int kv_heads,
+                 int d, int dv, int vs_row, int page_size, const ScoreRule& rule, cudaStream_t s) {
   const size_t bytes = smem_bytes(d, dv);
-  auto kernel = attention_scored_kernel<T, A>;
+  auto kernel = attention_scored_kernel<T, A, MAX_D>;
   static bool raised = false;
   if (bytes > 48 * 1024 && !raised) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(MAX_D, MAX_D));
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT);
     if (err != cudaSuccess) return fail(100, "paged_attention_scored: %s", cudaGetErrorString(err));
     raised = true;
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, heads, seqs);
   launch_kernel(kernel, grid, THREADS, bytes, s, (T*)out, (const T*)q, (const T*)keys, (const T*)values, block_table,
-                table_width, q_start, q_pos0, kv_len, heads, kv_heads, d, dv, page_size, rule);
+                table_width, q_start, q_pos0, kv_len, heads, kv_heads, d, dv, vs_row, page_size, rule);
   return check_launch("paged_attention_scored");
+}
+
+template <typename T, typename A>
+int launch(void* out, const void* q, const void* keys, const void* values, const int* block_table, int table_width,
+           const int* q_start, const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads, int kv_heads,
+           int d, int dv, int vs_row, int page_size, const ScoreRule& rule, cudaStream_t s) {
+#define PAE_SIZED(MAXD)                                                                                             \
+  if (dv <= MAXD)                                                                                                   \
+    return launch_sized<T, A, MAXD>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, \
+                                    max_q_len, heads, kv_heads, d, dv, vs_row, page_size, rule, s);
+  PAE_SIZED(64) PAE_SIZED(128) PAE_SIZED(256) PAE_SIZED(512)
+#undef PAE_SIZED
+  return fail(2, "paged_attention_scored: value heads of %d channels", dv);
 }
 
 }  // namespace
 
 // out [tokens, heads, dv]; q [tokens, heads, d]; keys [pages, kv_heads, page_size, d]; values
-// [pages, kv_heads, page_size, dv]; temp, r1, r2, sink float32 [heads] or null; cap 0: no cap.
+// [pages, kv_heads, page_size, dv], or the keys themselves (the same pointer: a key row's first dv
+// channels are its value; dv <= d); temp, r1, r2, sink float32 [heads] or null; cap 0: no cap.
 PAE_EXPORT int pae_paged_attention_scored(void* out, const void* q, const void* keys, const void* values,
                                           const int* block_table, int table_width, const int* q_start,
                                           const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads,
@@ -212,8 +232,10 @@ PAE_EXPORT int pae_paged_attention_scored(void* out, const void* q, const void* 
                                           const float* temp, const float* r1, const float* r2, const float* sink,
                                           int window, int keep_first, int dtype, void* stream) {
   if (seqs == 0 || max_q_len == 0) return 0;
-  if (d < 1 || dv < 1 || d > MAX_D || dv > MAX_D)
-    return fail(2, "paged_attention_scored: head sizes %d and %d are outside [1, %d]", d, dv, MAX_D);
+  if (d < 1 || dv < 1 || dv > MOST_CHANNELS || smem_bytes(d, dv) > SMEM_LIMIT)
+    return fail(2, "paged_attention_scored: head sizes %d and %d (values up to %d; both must fit shared memory)", d, dv, MOST_CHANNELS);
+  const int vs_row = values == keys ? d : dv;
+  if (values == keys && dv > d) return fail(2, "paged_attention_scored: values inside keys of %d channels cannot have %d", d, dv);
   if (kv_heads < 1 || heads % kv_heads) return fail(2, "paged_attention_scored: %d heads over %d kv heads", heads, kv_heads);
   if (heads > 65535 || seqs > 65535) return fail(3, "paged_attention_scored: %d heads x %d requests exceed one launch", heads, seqs);
   if (page_size < 1) return fail(2, "paged_attention_scored: page size %d", page_size);
@@ -223,10 +245,10 @@ PAE_EXPORT int pae_paged_attention_scored(void* out, const void* q, const void* 
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
     return launch<float, double>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len, heads,
-                         kv_heads, d, dv, page_size, rule, s);
+                         kv_heads, d, dv, vs_row, page_size, rule, s);
   if (dtype == kBF16)
     return launch<__nv_bfloat16, float>(out, q, keys, values, block_table, table_width, q_start, q_pos0, kv_len, seqs, max_q_len,
-                                 heads, kv_heads, d, dv, page_size, rule, s);
+                                 heads, kv_heads, d, dv, vs_row, page_size, rule, s);
   return fail(1, "paged_attention_scored: unknown dtype %d", dtype);
 }
 

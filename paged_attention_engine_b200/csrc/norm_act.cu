@@ -21,26 +21,74 @@ __device__ __forceinline__ double block_sum(double v, double* scratch) {
   return total;
 }
 
-// out[t, :] = table[id, :] + positions_table[p, :], float32. A negative id stands for the token
-// that the request sampled in the step before (last_token[state_slot[seq_index[t]]]).
+// out[t, :] = token_scale * table[id, :] + position_scale * positions_table[p, :], float32 (no
+// position table: the first term alone). A negative id stands for the token that the request
+// sampled in the step before (last_token[state_slot[seq_index[t]]]).
 template <typename T>
 __global__ void embedding_positions_kernel(float* __restrict__ out, const T* __restrict__ table,
                                            const T* __restrict__ position_table, const int* __restrict__ ids,
                                            const int* __restrict__ positions, const int* __restrict__ last_token,
                                            const int* __restrict__ state_slot, const int* __restrict__ seq_index,
-                                           int rows, int max_positions, int width, float position_scale) {
+                                           int rows, int max_positions, int width, float position_scale,
+                                           float token_scale) {
   dependent_launch_prologue();
   const int t = blockIdx.x;
   int src = ids[t];
   if (src < 0 && last_token != nullptr) src = last_token[state_slot[seq_index[t]]];
-  const int p = positions[t];
   const bool ok = src >= 0 && src < rows;
-  const bool pos_ok = p >= 0 && p < max_positions;
   const T* from = table + (size_t)(ok ? src : 0) * width;
-  const T* pos = position_table + (size_t)(pos_ok ? p : 0) * width;
   float* to = out + (size_t)t * width;
+  if (position_table == nullptr) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = ok ? token_scale * to_float(from[i]) : 0.f;
+    return;
+  }
+  const int p = positions[t];
+  const bool pos_ok = p >= 0 && p < max_positions;
+  const T* pos = position_table + (size_t)(pos_ok ? p : 0) * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x)
-    to[i] = (ok ? to_float(from[i]) : 0.f) + (pos_ok ? position_scale * to_float(pos[i]) : 0.f);
+    to[i] = (ok ? token_scale * to_float(from[i]) : 0.f) + (pos_ok ? position_scale * to_float(pos[i]) : 0.f);
+}
+
+// y = x / sqrt(mean(x^2) + eps) * w, from float32 or the engine's element type into either; the
+// sum of squares is double, the rest float32, one rounding at the end.
+template <typename TI, typename TO>
+__global__ void rms_norm_cast_kernel(TO* __restrict__ out, const TI* __restrict__ x, const float* __restrict__ weight,
+                                     int width, float eps) {
+  dependent_launch_prologue();
+  __shared__ double scratch[32];
+  const TI* row = x + (size_t)blockIdx.x * width;
+  double squares = 0.0;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const double v = (double)to_float(row[i]);
+    squares = fma(v, v, squares);
+  }
+  const float inv = (float)(1.0 / sqrt(block_sum(squares, scratch) / (double)width + (double)eps));
+  TO* to = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from_float<TO>(to_float(row[i]) * inv * weight[i]);
+}
+
+// The middle of a gated feed-forward whose gate and up projections are clamped:
+//   g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)
+// for rows that hold the gate in columns [0, I) and the up projection in [I, 2I).
+template <typename TI, typename TO>
+__global__ void clamped_glu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_up, long long total, int inter,
+                                   float limit, float alpha) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / inter;
+  const int c = (int)(i - t * inter);
+  const float g = fminf(to_float(gate_up[t * 2 * inter + c]), limit);
+  const float u = fminf(fmaxf(to_float(gate_up[t * 2 * inter + inter + c]), -limit), limit);
+  out[i] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+// x <- cap * tanh(x / cap), float32 in place.
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  x[i] = cap * tanhf(x[i] / cap);
 }
 
 // y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared deviations. One block
@@ -154,17 +202,17 @@ int row_threads(int width) { return width >= 2048 ? 512 : (width >= 1024 ? 256 :
 PAE_EXPORT int pae_embedding_positions(float* out, const void* table, const void* position_table, const int* ids,
                                        const int* positions, const int* last_token, const int* state_slot,
                                        const int* seq_index, int n, int rows, int max_positions, int width,
-                                       float position_scale, int dtype, void* stream) {
+                                       float position_scale, float token_scale, int dtype, void* stream) {
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = row_threads(width);
   if (dtype == kF32)
     launch_kernel(embedding_positions_kernel<float>, n, threads, 0, s, out, (const float*)table, (const float*)position_table,
-                  ids, positions, last_token, state_slot, seq_index, rows, max_positions, width, position_scale);
+                  ids, positions, last_token, state_slot, seq_index, rows, max_positions, width, position_scale, token_scale);
   else if (dtype == kBF16)
     launch_kernel(embedding_positions_kernel<__nv_bfloat16>, n, threads, 0, s, out, (const __nv_bfloat16*)table,
                   (const __nv_bfloat16*)position_table, ids, positions, last_token, state_slot, seq_index, rows,
-                  max_positions, width, position_scale);
+                  max_positions, width, position_scale, token_scale);
   else
     return fail(1, "embedding_positions: unknown dtype %d", dtype);
   return check_launch("embedding_positions");
@@ -205,6 +253,54 @@ PAE_EXPORT int pae_layer_norm(void* out, const void* x, const float* weight, con
   else
     return fail(1, "layer_norm: element types in=%d out=%d are not supported", in_dtype, out_dtype);
   return check_launch("layer_norm");
+}
+
+// x float32 or bfloat16 [rows, width] -> out float32 or bfloat16; weight float32.
+PAE_EXPORT int pae_rms_norm_cast(void* out, const void* x, const float* weight, int rows, int width, float eps,
+                                 int in_dtype, int out_dtype, void* stream) {
+  if (rows == 0 || width == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = row_threads(width);
+  using bf = __nv_bfloat16;
+  const int key = in_dtype * 10 + out_dtype;
+  if (key == 0)
+    launch_kernel(rms_norm_cast_kernel<float, float>, rows, threads, 0, s, (float*)out, (const float*)x, weight, width, eps);
+  else if (key == 1)
+    launch_kernel(rms_norm_cast_kernel<float, bf>, rows, threads, 0, s, (bf*)out, (const float*)x, weight, width, eps);
+  else if (key == 10)
+    launch_kernel(rms_norm_cast_kernel<bf, float>, rows, threads, 0, s, (float*)out, (const bf*)x, weight, width, eps);
+  else if (key == 11)
+    launch_kernel(rms_norm_cast_kernel<bf, bf>, rows, threads, 0, s, (bf*)out, (const bf*)x, weight, width, eps);
+  else
+    return fail(1, "rms_norm_cast: element types in=%d out=%d are not supported", in_dtype, out_dtype);
+  return check_launch("rms_norm_cast");
+}
+
+// gate_up [tokens, 2 * inter] in in_dtype -> out [tokens, inter] in out_dtype.
+PAE_EXPORT int pae_clamped_glu(void* out, const void* gate_up, int tokens, int inter, float limit, float alpha,
+                               int in_dtype, int out_dtype, void* stream) {
+  const long long total = (long long)tokens * inter;
+  if (total == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  using bf = __nv_bfloat16;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const int key = in_dtype * 10 + out_dtype;
+  if (key == 0)
+    launch_kernel(clamped_glu_kernel<float, float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, total, inter, limit, alpha);
+  else if (key == 1)
+    launch_kernel(clamped_glu_kernel<float, bf>, blocks, 256, 0, s, (bf*)out, (const float*)gate_up, total, inter, limit, alpha);
+  else if (key == 11)
+    launch_kernel(clamped_glu_kernel<bf, bf>, blocks, 256, 0, s, (bf*)out, (const bf*)gate_up, total, inter, limit, alpha);
+  else
+    return fail(1, "clamped_glu: element types in=%d out=%d are not supported", in_dtype, out_dtype);
+  return check_launch("clamped_glu");
+}
+
+PAE_EXPORT int pae_softcap(float* x, long long total, float cap, void* stream) {
+  if (total == 0) return 0;
+  if (!(cap > 0.f)) return fail(2, "softcap: the cap %g is not positive", (double)cap);
+  launch_kernel(softcap_kernel, (unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream, x, total, cap);
+  return check_launch("softcap");
 }
 
 PAE_EXPORT int pae_gelu(void* out, const void* x, long long total, int kind, int dtype, void* stream) {

@@ -38,7 +38,7 @@ class ReplayError(RuntimeError):
 class Replayer:
     """Runs trace records against one engine, cache and runner."""
 
-    def __init__(self, engine: Engine, max_tokens: int, block_size: int = 16, max_live: int = 8) -> None:
+    def __init__(self, engine: Engine, max_tokens: int, block_size: int = 16, max_live: int = 4) -> None:
         self.engine = engine
         self.block_size = block_size
         self.max_live = max_live
@@ -78,7 +78,7 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="tokens that live requests hold at most, each rounded up to whole pages")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per page")
-    parser.add_argument("--max-live", type=int, default=8, help="requests that may be live at a time")
+    parser.add_argument("--max-live", type=int, default=4, help="requests that may be live at a time (state slots)")
     args = parser.parse_args(argv)
 
     torch.backends.cuda.matmul.allow_tf32 = False

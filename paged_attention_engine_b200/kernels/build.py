@@ -50,6 +50,9 @@ FAMILIES: dict[str, list[str]] = {
     "attention_scored": ["attention_scored.cu", "common.cuh"],
     "attention_scored_mma": ["attention_scored_mma.cu", "attention_mma.cuh", "common.cuh"],
     "delta_rule": ["delta_rule.cu", "common.cuh"],
+    "head_prep": ["head_prep.cu", "common.cuh"],
+    "matrix_memory": ["matrix_memory.cu", "common.cuh"],
+    "linear_heads": ["linear_heads.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

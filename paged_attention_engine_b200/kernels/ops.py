@@ -501,11 +501,17 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k, activati
     return out
 
 
-def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, amplitude: float = 1.0) -> torch.Tensor:
+    """float32 [tokens, 2 * half]: amplitude * cos(position * inv_freq), then amplitude * sin of the same."""
     _need(positions, "rotary_table: positions", torch.int32)
     _need(inv_freq, "rotary_table: inv_freq", torch.float32)
     half = inv_freq.numel()
     table = torch.empty((positions.numel(), 2 * half), dtype=torch.float32, device=positions.device)
+    if amplitude != 1.0:
+        lib = _lib("head_prep")
+        _check(lib, lib.pae_rotary_table_amplitude(_ptr(table), _ptr(positions), _ptr(inv_freq), positions.numel(), half,
+                                                   float(amplitude), _stream()))
+        return table
     lib = _lib("elementwise")
     _check(lib, lib.pae_rotary_table(_ptr(table), _ptr(positions), _ptr(inv_freq), (positions.numel()),
                                      half, _stream()))
@@ -855,8 +861,182 @@ def embedding_positions(ids, positions, table, position_table, feedback=None, po
     lib = _lib("norm_act")
     _check(lib, lib.pae_embedding_positions(_ptr(out), _ptr(table), _ptr(position_table), _ptr(ids), _ptr(positions),
                                             _ptr(last_token), _ptr(state_slot), _ptr(seq_index), ids.numel(),
-                                            table.shape[0], position_table.shape[0], table.shape[1], position_scale,
+                                            table.shape[0], position_table.shape[0], table.shape[1], position_scale, 1.0,
                                             _code(table), _stream()))
+    return out
+
+
+def embedding_scaled(ids, table, scale: float, feedback=None) -> torch.Tensor:
+    """float32 [tokens, width]: scale * table[id]. `feedback` as in `embedding`."""
+    _need(table, "embedding_scaled: table")
+    _need(ids, "embedding_scaled: ids", torch.int32)
+    last_token, state_slot, seq_index = feedback if feedback is not None else (None, None, None)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_embedding_positions(_ptr(out), _ptr(table), None, _ptr(ids), None, _ptr(last_token), _ptr(state_slot),
+                                            _ptr(seq_index), ids.numel(), table.shape[0], 0, table.shape[1], 0.0, float(scale),
+                                            _code(table), _stream()))
+    return out
+
+
+def rms_norm_cast(x, weight: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight over the last axis; x float32 or the engine's dtype, the
+    result in `out_dtype` (x's when None)."""
+    x = materialized(x)
+    _need(x, "rms_norm_cast: x")
+    _need(weight, "rms_norm_cast: weight", torch.float32)
+    width = x.shape[-1]
+    if weight.numel() != width:
+        raise KernelError(f"rms_norm_cast: weight of {weight.numel()} for rows of {width}")
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    rows = x.numel() // width if x.numel() else 0
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_rms_norm_cast(_ptr(out), _ptr(x), _ptr(weight), rows, width, eps, _code(x), _code(out), _stream()))
+    return out
+
+
+def clamped_glu(gate_up, limit: float, alpha: float, out_dtype=None) -> torch.Tensor:
+    """g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), for
+    rows [tokens, 2 I] that hold the gate in columns [0, I) and the up projection in [I, 2 I)."""
+    gate_up = materialized(gate_up)
+    _need(gate_up, "clamped_glu: gate_up")
+    tokens, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"clamped_glu: rows of {two_i} do not split into gate and up")
+    out = torch.empty((tokens, two_i // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_clamped_glu(_ptr(out), _ptr(gate_up), tokens, two_i // 2, float(limit), float(alpha), _code(gate_up),
+                                    _code(out), _stream()))
+    return out
+
+
+def softcap(logits, cap: float) -> torch.Tensor:
+    """cap * tanh(logits / cap), float32, in place."""
+    logits = materialized(logits)
+    _need(logits, "softcap: logits", torch.float32)
+    lib = _lib("norm_act")
+    _check(lib, lib.pae_softcap(_ptr(logits), logits.numel(), float(cap), _stream()))
+    return logits
+
+
+def head_prep(proj, *, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, q_dim: int, k_dim: int, value_dim: int,
+              q_norm, k_norm, q_span: int, k_span: int, eps: float, table, interleaved: bool, q_rot0: int, k_rot0: int,
+              slots, keys, values, page_size: int, out_dtype) -> torch.Tensor:
+    """From a fused projection [tokens, ld] to attention's operands (csrc/head_prep.cu): every
+    query head (q_dim channels at q_off) and key head (k_dim channels at k_off) is RMS-normed over
+    its first q_span / k_span channels with the weight q_norm / k_norm (None: not normed), the span
+    of `table.shape[1]` channels from q_rot0 / k_rot0 is rotated by the table (pairs (i, i + half),
+    or (2i, 2i + 1) when `interleaved`), the queries are returned as [tokens, heads * q_dim] in
+    `out_dtype`, and keys and values (value_dim channels at v_off; `values` None: none) are written
+    to their pages at `slots` (None: nothing is written and kv_heads is ignored)."""
+    proj = materialized(proj)
+    _need(proj, "head_prep: projection")
+    tokens, ld = proj.shape
+    writes = slots is not None and kv_heads > 0
+    need = max(q_off + heads * q_dim, (k_off + kv_heads * k_dim) if writes else 0,
+               (v_off + kv_heads * value_dim) if writes and values is not None else 0)
+    if need > ld:
+        raise KernelError(f"head_prep: columns up to {need} of rows of {ld}")
+    for name, t, n in (("q_norm", q_norm, q_span), ("k_norm", k_norm, k_span)):
+        if t is not None:
+            _need(t, f"head_prep: {name}", torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"head_prep: {name} has {t.numel()} numbers for a span of {n}")
+    dims = 0
+    if table is not None:
+        _need(table, "head_prep: table", torch.float32)
+        if table.shape[0] != tokens:
+            raise KernelError(f"head_prep: a table of {table.shape[0]} rows for {tokens} tokens")
+        dims = int(table.shape[1])
+    if writes:
+        _need(slots, "head_prep: slots", torch.int32)
+        _need(keys, "head_prep: keys", out_dtype)
+        if values is not None:
+            _need(values, "head_prep: values", out_dtype)
+    q = torch.empty((tokens, heads * q_dim), dtype=out_dtype, device=proj.device)
+    lib = _lib("head_prep")
+    _set_bounds("head_prep", keys if writes else None)
+    _check(lib, lib.pae_head_prep(
+        _ptr(q), _ptr(keys if writes else None), _ptr(values if writes else None), _ptr(proj), ld, q_off, k_off, v_off, tokens,
+        heads, kv_heads if writes else 0, q_dim, k_dim, value_dim if values is not None else 0, _ptr(q_norm), q_span,
+        _ptr(k_norm), k_span, float(eps), _ptr(table), dims, 1 if interleaved else 0, q_rot0, k_rot0,
+        _ptr(slots if writes else None), page_size, _code(proj), _DTYPE_CODE[out_dtype], _stream()))
+    return q
+
+
+def sigmoid_gate(x, gate_proj, gate_off: int) -> torch.Tensor:
+    """x * sigmoid(gate_proj[:, gate_off : gate_off + x.shape[1]])."""
+    x = materialized(x)
+    gate_proj = materialized(gate_proj)
+    _need(x, "sigmoid_gate: x")
+    _need(gate_proj, "sigmoid_gate: gate")
+    if gate_proj.shape[0] != x.shape[0]:
+        raise KernelError(f"sigmoid_gate: {x.shape[0]} rows and {gate_proj.shape[0]} rows of gates")
+    out = torch.empty_like(x)
+    lib = _lib("head_prep")
+    _check(lib, lib.pae_sigmoid_gate(_ptr(out), _ptr(x), _ptr(gate_proj), x.shape[0], x.shape[1], gate_proj.shape[1], gate_off,
+                                     _code(x), _code(gate_proj), _stream()))
+    return out
+
+
+def linear_heads(x, weight, heads: int, in_stride: int, tail: int = 0) -> torch.Tensor:
+    """One product per head (csrc/linear_heads.cu): x [tokens, heads * in_stride], of which a head's
+    first K channels are the operand and the next `tail` pass through; weight [heads, N, K] ->
+    [tokens, heads * (N + tail)]."""
+    x = materialized(x)
+    _need(x, "linear_heads: x")
+    _need(weight, "linear_heads: weight", x.dtype)
+    if weight.dim() != 3 or weight.shape[0] != heads:
+        raise KernelError(f"linear_heads: weight is {tuple(weight.shape)} for {heads} heads")
+    n, k = int(weight.shape[1]), int(weight.shape[2])
+    if x.shape[1] != heads * in_stride or k + tail > in_stride:
+        raise KernelError(f"linear_heads: rows of {x.shape[1]} for {heads} heads of {k} + {tail} channels at a stride of {in_stride}")
+    out = torch.empty((x.shape[0], heads * (n + tail)), dtype=x.dtype, device=x.device)
+    lib = _lib("linear_heads")
+    _check(lib, lib.pae_linear_heads(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], heads, n, k, tail, x.shape[1], in_stride,
+                                     out.shape[1], n + tail, _code(x), _stream()))
+    return out
+
+
+def matrix_memory(proj, offsets, i_bias, f_bias, norm_weight, state, q_start, state_slot, num_seqs: int, num_heads: int,
+                  head_dim: int, value_dim: int, gate_cap: float, q_scale: float, norm_eps: float, out_dtype) -> torch.Tensor:
+    """The matrix memory (mLSTM) over the step's tokens, from and into the per-request state (float32
+    [slots, heads, head_dim * (value_dim + 1) + 1]): see csrc/matrix_memory.cu. `proj` float32
+    [tokens, ld] holds q, k, v, the output gate's and the two gates' projections at `offsets` =
+    (q, k, v, g, i, f). Returns rms_norm_per_head(o) * norm_weight * sigmoid(g) as [tokens, heads *
+    value_dim] in `out_dtype`."""
+    proj = materialized(proj)
+    _need(proj, "matrix_memory: projections", torch.float32)
+    _need(state, "matrix_memory: state", torch.float32)
+    for name, t, n in (("i bias", i_bias, num_heads), ("f bias", f_bias, num_heads), ("norm weight", norm_weight, num_heads * value_dim)):
+        _need(t, f"matrix_memory: {name}", torch.float32)
+        if t.numel() != n:
+            raise KernelError(f"matrix_memory: {name} has {t.numel()} numbers, {n} are needed")
+    _need(q_start, "matrix_memory: q_start", torch.int32)
+    _need(state_slot, "matrix_memory: state_slot", torch.int32)
+    tokens, ld = proj.shape
+    lib = _lib("matrix_memory")
+    per_head = lib.pae_matrix_memory_state_floats(head_dim, value_dim)
+    if tuple(state.shape[1:]) != (num_heads, per_head):
+        raise KernelError(f"matrix_memory: state rows are {tuple(state.shape[1:])}, ({num_heads}, {per_head}) is needed")
+    q_off, k_off, v_off, g_off, i_off, f_off = offsets
+    for off, width in ((q_off, num_heads * head_dim), (k_off, num_heads * head_dim), (v_off, num_heads * value_dim),
+                       (g_off, num_heads * value_dim), (i_off, num_heads), (f_off, num_heads)):
+        if off < 0 or off + width > ld:
+            raise KernelError(f"matrix_memory: columns {off}..{off + width} of rows of {ld}")
+    # Few (request, head) pairs leave SMs idle: a head's value columns are shared out over blocks
+    # (a column's recurrence needs no other column), each at least a warp wide.
+    splits, most, sms = 1, lib.pae_matrix_memory_max_splits(value_dim), _sm_count(proj.device)
+    while num_seqs * num_heads * splits < sms and splits * 2 <= most:
+        splits *= 2
+    o = torch.empty((tokens, num_heads * value_dim), dtype=torch.float32, device=proj.device)
+    carry = torch.empty(num_seqs * num_heads * (head_dim + 1), dtype=torch.float32, device=proj.device)
+    _check(lib, lib.pae_matrix_memory_scan(_ptr(o), _ptr(state), _ptr(carry), _ptr(proj), ld, q_off, k_off, v_off, i_off, f_off,
+                                           _ptr(i_bias), _ptr(f_bias), _ptr(q_start), _ptr(state_slot), num_seqs, num_heads,
+                                           head_dim, value_dim, splits, float(gate_cap), float(q_scale), _stream()), 2)
+    out = torch.empty((tokens, num_heads * value_dim), dtype=out_dtype, device=proj.device)
+    _check(lib, lib.pae_matrix_memory_output(_ptr(out), _ptr(o), _ptr(proj), ld, g_off, _ptr(norm_weight), tokens, num_heads,
+                                             value_dim, float(norm_eps), _DTYPE_CODE[out_dtype], _stream()))
     return out
 
 
@@ -965,7 +1145,7 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
         raise KernelError(f"paged_attention_scored: q rows of {q.shape[1]} for {num_heads} heads of {head_dim}")
     out = torch.empty((tokens, num_heads * value_dim), dtype=q.dtype, device=q.device)
     if (q.dtype == torch.bfloat16 and use_tensor_cores and head_dim in (32, 64, 128) and value_dim in (32, 64, 128)
-            and form != "simt"):
+            and form != "simt" and values.data_ptr() != keys.data_ptr()):
         lib = _lib("attention_scored_mma")
         _set_bounds("attention_scored_mma", keys)
         # A request that brings one token is one row of one block per head: its keys are shared out

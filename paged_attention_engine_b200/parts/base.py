@@ -80,13 +80,16 @@ class TensorSpec:
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values of a mixer: `window` 0 keeps all of them, w > 0 the last w and, before
-    them, the first `keep_first`. `value_dim` 0: values have the keys' head size."""
+    them, the first `keep_first`. `value_dim` 0: values have the keys' head size.
+    `values_in_keys`: a key row's first `value_dim` channels are its value, so the pages hold
+    keys only (a latent that is key and value at once)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
     keep_first: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

@@ -72,3 +72,36 @@ class DenseMLP(Part):
         ops = self.ops
         hidden = ops.linear(x, self.up_weight, None, activation=self.activation)     # the activation in the product's epilogue
         return ops.linear(hidden, self.down_weight, None, residual, out_dtype=residual.dtype if residual is not None else None)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(Part):
+    """down(g * sigmoid(alpha * g) * (u + 1)) with g = min(gate(x), limit) and u = clamp(up(x),
+    -limit, limit); all three projections have biases. params: hidden_size, intermediate_size,
+    limit, alpha. tensors: gate, up [intermediate, hidden], down [hidden, intermediate] and
+    gate.b, up.b, down.b. Gate and up are one product (float32 out: the clamps and the
+    activation see unrounded sums); the down projection adds its bias and the residual in its
+    epilogue and leaves the residual's dtype."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        hidden, inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        name = spec.tensor_name
+        return [TensorSpec(name("gate"), (inter, hidden), "matrix"), TensorSpec(name("gate.b"), (inter,), "vector"),
+                TensorSpec(name("up"), (inter, hidden), "matrix"), TensorSpec(name("up.b"), (inter,), "vector"),
+                TensorSpec(name("down"), (hidden, inter), "matrix"), TensorSpec(name("down.b"), (hidden,), "vector")]
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.limit, self.alpha = float(spec.params["limit"]), float(spec.params["alpha"])
+        name = spec.tensor_name
+        # rows [0, I) are the gate and rows [I, 2I) the up projection
+        self.gate_up_weight = torch.cat([tensors.pop(name("gate")), tensors.pop(name("up"))], dim=0).contiguous()
+        self.gate_up_bias = torch.cat([tensors.pop(name("gate.b")), tensors.pop(name("up.b"))], dim=0).contiguous()
+        self.down_weight, self.down_bias = tensors.pop(name("down")), tensors.pop(name("down.b"))
+
+    def forward(self, ctx, x, residual):
+        ops = self.ops
+        gate_up = ops.linear(x, self.gate_up_weight, self.gate_up_bias, None, out_dtype=torch.float32)
+        hidden = ops.clamped_glu(gate_up, self.limit, self.alpha, self.runtime.dtype)
+        return ops.linear(hidden, self.down_weight, self.down_bias, residual, out_dtype=residual.dtype)

@@ -36,8 +36,8 @@ class TokenEmbedding(Part):
 
 @HEADS.register("lm_head")
 class LMHead(Part):
-    """params: vocab_size, hidden_size, tied_to (a tensor's full name, or None).
-    tensors: weight [vocab, hidden] unless tied."""
+    """params: vocab_size, hidden_size, tied_to (a tensor's full name, or None), softcap (0 or
+    absent: none; c: logits <- c tanh(logits / c), in float32). tensors: weight [vocab, hidden] unless tied."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
@@ -49,9 +49,11 @@ class LMHead(Part):
         super().__init__(spec, tensors, runtime)
         tied = spec.params.get("tied_to")
         self.weight = tensors[tied] if tied else tensors[spec.tensor_name("weight")]
+        self.softcap = float(spec.params.get("softcap") or 0.0)
 
     def forward(self, ctx, rows):
-        return self.ops.linear(rows, self.weight, None, None, out_dtype=torch.float32)
+        logits = self.ops.linear(rows, self.weight, None, None, out_dtype=torch.float32)
+        return self.ops.softcap(logits, self.softcap) if self.softcap else logits
 
 
 @EMBEDDINGS.register("token_position_embedding")
@@ -78,3 +80,24 @@ class TokenPositionEmbedding(Part):
     def forward(self, ctx):
         return self.ops.embedding_positions(ctx.token_ids, ctx.positions, self.weight, self.positions,
                                             getattr(ctx, "feedback", None), self.position_scale)
+
+
+@EMBEDDINGS.register("scaled_token_embedding")
+class ScaledTokenEmbedding(Part):
+    """scale * table[token] as a float32 residual stream. params: vocab_size, hidden_size, scale.
+    tensors: weight [vocab, hidden]."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
+        return [TensorSpec(spec.tensor_name("weight"), (int(spec.params["vocab_size"]), int(spec.params["hidden_size"])), "matrix")]
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight = tensors[spec.tensor_name("weight")]
+        self.scale = float(spec.params.get("scale", 1.0))
+
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        return num_tokens * self.weight.shape[1] * self.weight.element_size()
+
+    def forward(self, ctx):
+        return self.ops.embedding_scaled(ctx.token_ids, self.weight, self.scale, getattr(ctx, "feedback", None))

@@ -11,7 +11,8 @@ from .base import NORMS, Part, TensorSpec
 
 @NORMS.register("rms_norm")
 class RMSNorm(Part):
-    """params: size, eps. tensors: weight [size]."""
+    """params: size, eps, out ("engine": the result is in the engine's dtype whatever x is, as a
+    float32 residual stream needs; default: x's dtype). tensors: weight [size]."""
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
@@ -21,8 +22,11 @@ class RMSNorm(Part):
         super().__init__(spec, tensors, runtime)
         self.eps = float(spec.params["eps"])
         self.weight = tensors[spec.tensor_name("weight")]
+        self.out_dtype = runtime.dtype if spec.params.get("out") == "engine" else None
 
     def forward(self, ctx, x):
+        if self.out_dtype is not None:
+            return self.ops.rms_norm_cast(x, self.weight, self.eps, self.out_dtype)
         return self.ops.rms_norm(x, self.weight, self.eps)
 
 
