@@ -272,6 +272,28 @@ def bidonex_pair(size: dict, window: int = 1024) -> tuple[dict, dict]:
     return bidonex, qwen
 
 
+def zugarax_config(size: dict, window: int = 1024, kv_rank: int = 512, rot_dim: int = 64) -> dict:
+    """Zugarax at the layer sizes of `size`: gated window attention, latent attention, gated window
+    attention, matrix memory, and so on; every latent layer after the first reads the first one's latent."""
+    mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    d = size["dim"]
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "kv_heads": size["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": window},
+        "rot": {"base": 10000.0, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "dim": d, "rot_dim": rot_dim, "vdim": d, "kv_rank": kv_rank, "scale": (d + rot_dim) ** -0.5,
+        "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    memory = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": size["heads"], "dim": d, "vdim": d, "gate_cap": 15.0}}
+    layers = []
+    for i in range(size["layers"]):
+        layer = json.loads(json.dumps((attention, latent, attention, memory)[i % 4]))
+        if i % 4 == 1 and i > 1:
+            layer["mixer"]["kv_from"] = 1
+        layers.append(layer)
+    return {"architecture": "Zugarax", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": size["width"] ** 0.5},
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers}
+
+
 def step_cache_bytes(cache, contexts) -> float:
     """Cache bytes that a decode step reads: per page group the keys and values a request can see
     (all of its context, or the window and the kept first keys), and every recurrent state
@@ -279,22 +301,25 @@ def step_cache_bytes(cache, contexts) -> float:
     size = cache.pools[0].element_size() if cache.pools else 2
     total = 0.0
     for g in cache.plan.groups:
-        per_token = len(g.entries) * g.num_kv_heads * (g.head_dim + g.value_head_dim) * size
+        per_token = len(g.entries) * g.stored_per_token * size
         total += per_token * sum(min(c, g.window + g.keep_first) if g.window else c for c in contexts)
     for state in cache.states.values():
         total += 2.0 * len(contexts) * state[0].numel() * state.element_size()
     return total
 
 
-def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes) -> dict:
+def bidonex_beside_qwen2(torch, peak: dict, steps: int, warmup: int, sizes, with_zugarax: bool = False) -> dict:
+    """Prefill and decode of the architectures at equal layer sizes; `with_zugarax` puts Zugarax
+    in front of Bidonex (the closest of the others: a float32 stream, windows, a recurrent layer) and Qwen2."""
     from paged_attention_engine_b200.engine.llm import Engine
     from paged_attention_engine_b200.sampling import SamplingRow
 
-    out: dict = {"only": "bidonex", "peaks": peak["source"], "sizes": {}}
+    out: dict = {"only": "zugarax" if with_zugarax else "bidonex", "peaks": peak["source"], "sizes": {}}
     for name in sizes:
         bidonex, qwen = bidonex_pair(BIDONEX_SIZES[name])
         rows: dict = {}
-        for arch, raw in (("bidonex", bidonex), ("qwen2", qwen)):
+        archs = (("zugarax", zugarax_config(BIDONEX_SIZES[name])),) if with_zugarax else ()
+        for arch, raw in archs + (("bidonex", bidonex), ("qwen2", qwen)):
             engine = Engine.from_random(raw, seed=0, dtype="bfloat16", device="cuda:0")
             row: dict = {"layers": BIDONEX_SIZES[name]["layers"], "weight_gb": round(engine.weight_bytes() / 1e9, 3)}
             for tokens in (512, 2048, 8192):
@@ -728,9 +753,9 @@ def main() -> int:
                         help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
     parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
-    parser.add_argument("--arch", choices=("qwen2", "bidonex"), default="qwen2",
+    parser.add_argument("--arch", choices=("qwen2", "bidonex", "zugarax"), default="qwen2",
                         help="with --only decode / prefill: the architecture that runs at the --shape's layer sizes")
-    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex"), default="all",
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b", "bidonex", "zugarax"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
@@ -759,9 +784,9 @@ def main() -> int:
     if args.only == "pressure32b":
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
         return 0
-    if args.only == "bidonex":
+    if args.only in ("bidonex", "zugarax"):
         sizes = ("1.5b", "7b") if args.shape == "1.5b" else (args.shape,)
-        print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes)))
+        print(json.dumps(bidonex_beside_qwen2(torch, peak, args.steps, warmup, sizes, with_zugarax=args.only == "zugarax")))
         return 0
     if args.only == "products":
         for row in time_products({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape], args.batch, torch, peak):
@@ -772,16 +797,16 @@ def main() -> int:
     if args.only != "all" and args.shape != "1.5b" and args.layers == MODEL["num_hidden_layers"]:
         args.layers = model["num_hidden_layers"]
     model["num_hidden_layers"] = args.layers
-    if args.arch == "bidonex" and args.only in ("decode", "prefill"):
+    if args.arch in ("bidonex", "zugarax") and args.only in ("decode", "prefill"):
         if args.shape not in BIDONEX_SIZES:
-            print(f"bench.py: --arch bidonex has the shapes {', '.join(BIDONEX_SIZES)}")
+            print(f"bench.py: --arch {args.arch} has the shapes {', '.join(BIDONEX_SIZES)}")
             return 2
         size = dict(BIDONEX_SIZES[args.shape])
         if args.layers != MODEL["num_hidden_layers"]:
             size["layers"] = args.layers
         args.layers = size["layers"]
         bidonex, model = bidonex_pair(size)
-        engine = Engine.from_random(bidonex, seed=0, dtype="bfloat16", device="cuda:0")
+        engine = Engine.from_random(zugarax_config(size) if args.arch == "zugarax" else bidonex, seed=0, dtype="bfloat16", device="cuda:0")
     else:
         engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
 

@@ -50,6 +50,7 @@ FAMILIES: dict[str, list[str]] = {
     "attention_scored": ["attention_scored.cu", "common.cuh"],
     "attention_scored_mma": ["attention_scored_mma.cu", "attention_mma.cuh", "common.cuh"],
     "delta_rule": ["delta_rule.cu", "common.cuh"],
+    "attention_latent_mma": ["attention_latent_mma.cu", "attention_mma.cuh", "common.cuh"],
     "head_prep": ["head_prep.cu", "common.cuh"],
     "matrix_memory": ["matrix_memory.cu", "common.cuh"],
     "linear_heads": ["linear_heads.cu", "common.cuh"],

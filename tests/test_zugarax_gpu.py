@@ -233,6 +233,37 @@ def test_attention_whose_values_are_the_leading_channels_of_its_keys(dtype, c, r
             q[start:start + count].reshape(count, -1).contiguous().to(DEV), keys, keys, _ints(table).view(1, width), _ints([0, count]),
             _ints([start]), _ints([start + count]), heads, 1, c + r, c, page, count, scale, max_kv_len=start + count, num_single=int(count == 1))
         _close(got.view(count, heads, c), want[start:start + count], dtype)
+        if dtype == torch.bfloat16:          # the CUDA-core kernel, whatever the sizes
+            same = ops.paged_attention_scored(
+                q[start:start + count].reshape(count, -1).contiguous().to(DEV), keys, keys, _ints(table).view(1, width),
+                _ints([0, count]), _ints([start]), _ints([start + count]), heads, 1, c + r, c, page, count, scale,
+                max_kv_len=start + count, num_single=int(count == 1), form="simt")
+            _close(same.view(count, heads, c), want[start:start + count], dtype)
+
+
+def test_latent_attention_on_tensor_cores_many_heads_long_contexts_and_batches():
+    """Sizes that the tensor-core kernel takes: more than 16 heads (two head groups for a single
+    token), contexts of many tiles shared out over blocks, single tokens beside portions."""
+    ops = _ops()
+    lib = ops._lib("attention_latent_mma")
+    for c, r, heads, page, T in ((64, 16, 20, 16, 300), (512, 64, 4, 16, 200), (128, 32, 6, 8, 530)):
+        assert lib.pae_attention_latent_mma_supports(c + r, c) == 1
+        rows, keys, table = _latent_rows(torch.bfloat16, T, c, r, page, -(-T // page) + 3, c + heads)
+        q = (torch.randn(T, heads, c + r) * 0.5).to(torch.bfloat16)
+        scale = 1.0 / math.sqrt(c + r)
+        want = plain.softmax_attention(q.double(), rows.double().view(T, 1, c + r), rows[:, :c].double().view(T, 1, c), scale,
+                                       rows=list(range(T - 40, T)))
+        width = len(table)
+        # a portion of 39 tokens, then the last token alone, as two requests over the same pages in one launch
+        q_rows = torch.cat([q[T - 40:T - 1], q[T - 1:]]).reshape(40, -1).contiguous().to(DEV)
+        got = ops.paged_attention_scored(
+            q_rows, keys, keys, _ints(table + table).view(2, width), _ints([0, 39, 40]), _ints([T - 40, T - 1]), _ints([T - 1, T]),
+            heads, 1, c + r, c, page, 39, scale, max_kv_len=T, num_single=1)
+        _close(got.view(40, heads, c), want[T - 40:], torch.bfloat16)
+        alone = ops.paged_attention_scored(
+            q[T - 1:].reshape(1, -1).contiguous().to(DEV), keys, keys, _ints(table).view(1, width), _ints([0, 1]), _ints([T - 1]),
+            _ints([T]), heads, 1, c + r, c, page, 1, scale, max_kv_len=T, num_single=1)
+        _close(alone.view(1, heads, c), want[T - 1:], torch.bfloat16)
 
 
 # --------------------------------------------------------------------------- #
