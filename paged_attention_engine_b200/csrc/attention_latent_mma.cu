@@ -317,7 +317,8 @@ PAE_EXPORT int pae_paged_attention_latent_mma(void* out, const void* q, const vo
   launch_kernel(latent_kernel, grid, 128, bytes, s, p);
   if (int err = check_launch("paged_attention_latent_mma")) return err;
   if (scratch != nullptr) {
-    launch_kernel(latent_merge_kernel, dim3(heads, seqs), 128, (size_t)splits * sizeof(float), s, p);
+    const int threads = dv >= 512 ? 512 : (dv + 31) / 32 * 32;       // a column a thread
+    launch_kernel(latent_merge_kernel, dim3(heads, seqs), threads, (size_t)splits * sizeof(float), s, p);
     return check_launch("paged_attention_latent_merge");
   }
   return 0;

@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(WARPS * 32) head_prep_kernel(const HeadPrep p)
   }
   const int page = slot >= 0 ? slot / p.page_size : 0, offset = slot >= 0 ? slot - page * p.page_size : 0;
   const int half = p.dims >> 1;
-  for (int unit = warp; unit < units; unit += WARPS) {
+  for (int unit = blockIdx.y * WARPS + warp; unit < units; unit += WARPS * gridDim.y) {
     const bool is_q = unit < p.heads, is_k = !is_q && unit < p.heads + p.kv_heads;
     const int index = is_q ? unit : (is_k ? unit - p.heads : unit - p.heads - p.kv_heads);
     const int d = is_q ? p.qd : (is_k ? p.kd : p.dv);
@@ -153,9 +153,12 @@ PAE_EXPORT int pae_head_prep(void* q_out, void* keys, void* values, const void* 
   cudaStream_t s = (cudaStream_t)stream;
   using bf = __nv_bfloat16;
   const int key = in_dtype * 10 + out_dtype;
-  if (key == 0) launch_kernel(head_prep_kernel<float, float>, tokens, WARPS * 32, smem, s, p);
-  else if (key == 1) launch_kernel(head_prep_kernel<float, bf>, tokens, WARPS * 32, smem, s, p);
-  else if (key == 11) launch_kernel(head_prep_kernel<bf, bf>, tokens, WARPS * 32, smem, s, p);
+  // few tokens: a warp per head, so that a decode step's handful of tokens still fills some SMs
+  const int units = heads + p.kv_heads * (values != nullptr && dv > 0 ? 2 : 1);
+  const dim3 grid(tokens, tokens < 64 ? (units + WARPS - 1) / WARPS : 1);
+  if (key == 0) launch_kernel(head_prep_kernel<float, float>, grid, WARPS * 32, smem, s, p);
+  else if (key == 1) launch_kernel(head_prep_kernel<float, bf>, grid, WARPS * 32, smem, s, p);
+  else if (key == 11) launch_kernel(head_prep_kernel<bf, bf>, grid, WARPS * 32, smem, s, p);
   else return fail(1, "head_prep: element types in=%d out=%d are not supported", in_dtype, out_dtype);
   return check_launch("head_prep");
 }

@@ -8,12 +8,15 @@
 //
 // Latent attention uses it twice: the queries' unrotated channels times the transposed key
 // expansion (the rotated channels pass through as the tail), and the attention's output over
-// the latent times the value expansion. On the CUDA cores, any sizes, float32 or bfloat16; a
-// float32 product sums in double as the plain product does. An output element sums its K
-// products in the same order whatever else is in the batch.
-#include "common.cuh"
+// the latent times the value expansion. Two kernels: on the CUDA cores, any sizes, float32 or
+// bfloat16 (a float32 product sums in double as the plain product does); and for bfloat16 with K a
+// multiple of 16 and 16-byte aligned heads on tensor cores (mma.sync m16n8k16, float32
+// accumulation, 64 tokens x 64 outputs a block). An output element sums its K products in the
+// same order whatever else is in the batch.
+#include "attention_mma.cuh"
 
 using namespace pae;
+using namespace pae_attention;
 
 namespace {
 
@@ -64,6 +67,82 @@ __global__ void __launch_bounds__(256) linear_heads_kernel(T* __restrict__ out, 
     }
 }
 
+// 64 tokens x 64 outputs of one head per block; a warp owns 16 tokens. K goes through shared
+// memory 32 channels at a time (rows padded by 16 bytes: conflict-free ldmatrix), two stages.
+constexpr int TM = 64, TN = 64, TK = 32, ROW_BYTES = TK * 2 + 16;
+
+__global__ void __launch_bounds__(128) linear_heads_mma_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w, int M, int N, int K, int tail,
+                                                               long long x_ld, int x_hs, long long o_ld, int o_hs) {
+  dependent_launch_prologue();
+  __shared__ __align__(128) uint8_t tiles[2][(TM + TN) * ROW_BYTES];
+  const int h = blockIdx.z, m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const __nv_bfloat16* xh = x + (size_t)h * x_hs;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  __nv_bfloat16* oh = out + (size_t)h * o_hs;
+  // a thread copies one 16-byte chunk of two rows of each operand per stage: 64 rows x 4 chunks
+  const int l_row = tid >> 2, l_chunk = tid & 3;
+  auto fetch = [&](int stage, int k0) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = l_row + half * 32;
+      uint8_t* a_dst = tiles[stage] + r * ROW_BYTES + l_chunk * 16;
+      uint8_t* b_dst = tiles[stage] + (TM + r) * ROW_BYTES + l_chunk * 16;
+      const bool k_ok = k0 + l_chunk * 8 < K;
+      if (m0 + r < M && k_ok) cp_async16(smem_u32(a_dst), xh + (size_t)(m0 + r) * x_ld + k0 + l_chunk * 8);
+      else *(uint4*)a_dst = make_uint4(0, 0, 0, 0);
+      if (n0 + r < N && k_ok) cp_async16(smem_u32(b_dst), wh + (size_t)(n0 + r) * K + k0 + l_chunk * 8);
+      else *(uint4*)b_dst = make_uint4(0, 0, 0, 0);
+    }
+  };
+  float acc[TN / 8][4];
+#pragma unroll
+  for (int n = 0; n < TN / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  const int steps = (K + TK - 1) / TK;
+  const int mid = lane >> 3, r8 = lane & 7;
+  fetch(0, 0);
+  cp_async_commit();
+  for (int s = 0; s < steps; ++s) {
+    if (s + 1 < steps) fetch((s + 1) & 1, (s + 1) * TK);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t base = smem_u32(tiles[s & 1]);
+#pragma unroll
+    for (int kk = 0; kk < TK / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, base + (warp * 16 + ((lane >> 3) & 1) * 8 + r8) * ROW_BYTES + (kk * 2 + (lane >> 4)) * 16);
+#pragma unroll
+      for (int n = 0; n < TN / 16; ++n) {
+        uint32_t b[4];
+        ldmatrix_x4(b, base + (TM + n * 16 + (mid >> 1) * 8 + r8) * ROW_BYTES + (kk * 2 + (mid & 1)) * 16);
+        mma_16816(acc[2 * n], a, b[0], b[1]);
+        mma_16816(acc[2 * n + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  const int c2 = (lane & 3) * 2;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = m0 + warp * 16 + (lane >> 2) + half * 8;
+    if (m >= M) continue;
+#pragma unroll
+    for (int n = 0; n < TN / 8; ++n) {
+      const int col = n0 + n * 8 + c2;
+      if (col < N) oh[(size_t)m * o_ld + col] = __float2bfloat16_rn(acc[n][half * 2]);
+      if (col + 1 < N) oh[(size_t)m * o_ld + col + 1] = __float2bfloat16_rn(acc[n][half * 2 + 1]);
+    }
+  }
+  if (blockIdx.x == 0 && tail > 0)
+    for (int e = tid; e < TM * tail; e += 128) {
+      const int r = e / tail, c = e - r * tail;
+      if (m0 + r < M) oh[(size_t)(m0 + r) * o_ld + N + c] = xh[(size_t)(m0 + r) * x_ld + K + c];
+    }
+}
+
 }  // namespace
 
 PAE_EXPORT int pae_linear_heads(void* out, const void* x, const void* w, int tokens, int heads, int n, int k, int tail,
@@ -71,9 +150,16 @@ PAE_EXPORT int pae_linear_heads(void* out, const void* x, const void* w, int tok
   if (tokens == 0 || heads == 0) return 0;
   if (n < 1 || k < 1 || tail < 0) return fail(2, "linear_heads: a product of %d x %d with a tail of %d", n, k, tail);
   if (heads > 65535 || (tokens + BM - 1) / BM > 65535) return fail(3, "linear_heads: %d heads x %d tokens exceed one launch", heads, tokens);
-  dim3 grid((n + BN - 1) / BN, (tokens + BM - 1) / BM, heads);
   cudaStream_t s = (cudaStream_t)stream;
   using bf = __nv_bfloat16;
+  if (dtype == kBF16 && k % 16 == 0 && x_ld % 8 == 0 && x_hs % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0 &&
+      (tokens + TM - 1) / TM <= 65535) {
+    dim3 tiles((n + TN - 1) / TN, (tokens + TM - 1) / TM, heads);
+    launch_kernel(linear_heads_mma_kernel, tiles, 128, 0, s, (bf*)out, (const bf*)x, (const bf*)w, tokens, n, k, tail, x_ld, x_hs,
+                  o_ld, o_hs);
+    return check_launch("linear_heads");
+  }
+  dim3 grid((n + BN - 1) / BN, (tokens + BM - 1) / BM, heads);
   if (dtype == kF32)
     launch_kernel(linear_heads_kernel<float, double>, grid, 256, 0, s, (float*)out, (const float*)x, (const float*)w, tokens, n, k,
                   tail, x_ld, x_hs, o_ld, o_hs);

@@ -12,7 +12,8 @@
 // as the augmented matrix [d][dv + 1] (column dv is n) followed by m, float32. A block owns one
 // (request, head, range of value columns); thread j keeps column j of S in shared memory (bank j:
 // no conflicts), and the last thread of every block keeps the column n, so n . q falls out of the
-// same loop as S^T q and every block can divide by itself. The tokens' q, k, v and gates come in
+// same loop as S^T q and every block can divide by itself (head sizes that are multiples of 16 up to
+// 128 take a second form of the kernel, further down, with the columns in registers). The tokens' q, k, v and gates come in
 // tiles of 16 tokens; the gates' transcendental functions are computed once per tile in parallel.
 // A token's arithmetic is the same instructions in the same order wherever a prompt was cut,
 // so the state is carried bit for bit across portions.
@@ -126,6 +127,118 @@ __global__ void matrix_memory_scan_kernel(const Scan p) {
   }
 }
 
+// The same recurrence for head sizes known at compile time: a thread keeps its column of S in
+// registers, a warp owns 32 value columns and needs no other warp (every warp keeps a copy of n,
+// spread over its lanes, and sums n . q by shuffles), so a token costs no barrier: D fused
+// multiply-adds on the column, D more for its read-out (four partial sums), and q and k from
+// shared memory, 16 bytes at a time.
+template <int D>
+__global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const Scan p) {
+  dependent_launch_prologue();
+  extern __shared__ __align__(16) float smem[];
+  constexpr int NJ = (D + 31) / 32;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int c0 = blockIdx.x * p.cols;                        // p.cols: a multiple of 32, the block's threads
+  const int first = p.q_start[b], count = p.q_start[b + 1] - first;
+  if (c0 >= p.dv || count <= 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int dv = p.dv, cols = p.cols;
+  const int col = c0 + tid;
+  const bool has_col = col < dv;
+  float* qs = smem;                                          // [TILE][D]
+  float* ks = qs + TILE * D;                                 // [TILE][D]
+  float* vs = ks + TILE * D;                                 // [TILE][cols]
+  float* gi = vs + TILE * cols;                              // [TILE]
+  float* gf = gi + TILE;                                     // [TILE]
+  const size_t per_head = (size_t)D * (dv + 1) + 1;
+  float* st = p.state + ((size_t)p.state_slot[b] * p.heads + h) * per_head;
+  float s[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) s[i] = has_col ? st[(size_t)i * (dv + 1) + col] : 0.f;
+  float n[NJ];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) n[j] = lane + 32 * j < D ? st[(size_t)(lane + 32 * j) * (dv + 1) + dv] : 0.f;
+  float m = st[per_head - 1];
+
+  for (int t0 = 0; t0 < count; t0 += TILE) {
+    const int n_tok = min(TILE, count - t0);
+    __syncthreads();                                         // the tile before is used up
+    for (int e = tid; e < n_tok * D; e += cols) {
+      const int t = e / D, i = e - t * D;
+      const float* row = p.proj + (size_t)(first + t0 + t) * p.ld;
+      qs[e] = row[p.q_off + h * D + i] * p.q_scale;
+      ks[e] = row[p.k_off + h * D + i];
+    }
+    for (int t = 0; t < n_tok; ++t)
+      vs[t * cols + tid] = has_col ? p.proj[(size_t)(first + t0 + t) * p.ld + p.v_off + h * dv + col] : 0.f;
+    if (tid < n_tok) {
+      const float* row = p.proj + (size_t)(first + t0 + tid) * p.ld;
+      const float a = row[p.i_off + h] + p.i_bias[h], g = row[p.f_off + h] + p.f_bias[h];
+      gi[tid] = p.cap * tanhf(a / p.cap);
+      const float z = p.cap * tanhf(g / p.cap);
+      gf[tid] = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));      // log sigmoid(z)
+    }
+    __syncthreads();
+    for (int t = 0; t < n_tok; ++t) {
+      const float li = gi[t], lf = gf[t];
+      const float m_new = fmaxf(lf + m, li);
+      const float keep = expf(lf + m - m_new), add = expf(li - m_new);
+      m = m_new;
+      const float* q = qs + t * D;
+      const float* k = ks + t * D;
+      float part = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int i = lane + 32 * j;
+        if (i < D) {
+          n[j] = fmaf(keep, n[j], add * k[i]);
+          part = fmaf(n[j], q[i], part);
+        }
+      }
+      part = warp_sum(part);
+      const float below = fmaxf(fabsf(part), expf(-m)) + 1e-6f;
+      const float av = add * vs[t * cols + tid];
+      float num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < D; i += 4) {
+        const float4 k4 = *(const float4*)(k + i), q4 = *(const float4*)(q + i);
+        s[i] = fmaf(keep, s[i], k4.x * av);
+        s[i + 1] = fmaf(keep, s[i + 1], k4.y * av);
+        s[i + 2] = fmaf(keep, s[i + 2], k4.z * av);
+        s[i + 3] = fmaf(keep, s[i + 3], k4.w * av);
+        num[0] = fmaf(s[i], q4.x, num[0]);
+        num[1] = fmaf(s[i + 1], q4.y, num[1]);
+        num[2] = fmaf(s[i + 2], q4.z, num[2]);
+        num[3] = fmaf(s[i + 3], q4.w, num[3]);
+      }
+      if (has_col) p.o[((size_t)(first + t0 + t) * p.heads + h) * dv + col] = ((num[0] + num[1]) + (num[2] + num[3])) / below;
+    }
+  }
+  if (has_col) {
+#pragma unroll
+    for (int i = 0; i < D; ++i) st[(size_t)i * (dv + 1) + col] = s[i];
+  }
+  // every block of a head read n and m of the state when it started: see the kernel above
+  if (blockIdx.x == 0 && warp == 0) {
+    float* to = p.carry + ((size_t)b * p.heads + h) * (D + 1);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < D) to[lane + 32 * j] = n[j];
+    if (lane == 0) to[D] = m;
+  }
+}
+
+template <int D>
+int launch_columns(Scan p, int seqs, int splits, cudaStream_t s) {
+  const int warps = (p.dv + 31) / 32;
+  int per_block = (warps + splits - 1) / splits;
+  per_block = per_block > 4 ? 4 : per_block;
+  p.cols = 32 * per_block;
+  const size_t smem = sizeof(float) * ((size_t)TILE * (2 * D + p.cols) + 2 * TILE);
+  launch_kernel(matrix_memory_scan_columns_kernel<D>, dim3((warps + per_block - 1) / per_block, p.heads, seqs), p.cols, smem, s, p);
+  return check_launch("matrix_memory_scan");
+}
+
 __global__ void matrix_memory_commit_kernel(const Scan p) {
   dependent_launch_prologue();
   const int h = blockIdx.x, b = blockIdx.y;
@@ -143,7 +256,7 @@ __global__ void matrix_memory_output_kernel(TO* __restrict__ out, const float* _
                                             int ld, int g_off, const float* __restrict__ weight, int heads, int dv, float eps) {
   dependent_launch_prologue();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int h = warp; h < heads; h += warps) {
+  for (int h = blockIdx.y * warps + warp; h < heads; h += warps * gridDim.y) {
     const float* row = o + ((size_t)t * heads + h) * dv;
     double squares = 0.0;
     for (int i = lane; i < dv; i += 32) squares = fma((double)row[i], (double)row[i], squares);
@@ -182,6 +295,22 @@ PAE_EXPORT int pae_matrix_memory_scan(float* o, float* state, float* carry, cons
   if (!(cap > 0.f)) return fail(2, "matrix_memory: the gates' cap %g is not positive", (double)cap);
   if (splits < 1 || splits > dv) return fail(2, "matrix_memory: %d splits of %d value columns", splits, dv);
   if (heads > 65535 || seqs > 65535) return fail(3, "matrix_memory: %d heads x %d requests exceed one launch", heads, seqs);
+  {
+    Scan p{o, state, carry, proj, i_bias, f_bias, q_start, state_slot, ld, q_off, k_off, v_off, i_off, f_off, heads, d, dv, 0, cap, q_scale};
+    cudaStream_t s = (cudaStream_t)stream;
+    int done = -1;
+    switch (d) {
+#define PAE_COLUMNS(DD) case DD: done = launch_columns<DD>(p, seqs, splits, s); break;
+      PAE_COLUMNS(16) PAE_COLUMNS(32) PAE_COLUMNS(48) PAE_COLUMNS(64) PAE_COLUMNS(80) PAE_COLUMNS(96) PAE_COLUMNS(112) PAE_COLUMNS(128)
+#undef PAE_COLUMNS
+      default: break;
+    }
+    if (done > 0) return done;
+    if (done == 0) {
+      launch_kernel(matrix_memory_commit_kernel, dim3(heads, seqs), 64, 0, s, p);
+      return check_launch("matrix_memory_commit");
+    }
+  }
   int cols = (dv + splits - 1) / splits;
   while (cols + 1 > 1024 || scan_smem(d, cols) > 200 * 1024) {        // narrower blocks until one fits
     if (cols == 1) return fail(2, "matrix_memory: heads of %d key channels do not fit shared memory", d);
@@ -208,10 +337,11 @@ PAE_EXPORT int pae_matrix_memory_output(void* out, const float* o, const float* 
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = heads >= 4 ? 128 : 32 * heads;
+  const dim3 grid(tokens, tokens < 64 ? (heads + 3) / 4 : 1);          // few tokens: a warp per head
   if (out_dtype == kF32)
-    launch_kernel(matrix_memory_output_kernel<float>, tokens, threads, 0, s, (float*)out, o, proj, ld, g_off, weight, heads, dv, eps);
+    launch_kernel(matrix_memory_output_kernel<float>, grid, threads, 0, s, (float*)out, o, proj, ld, g_off, weight, heads, dv, eps);
   else if (out_dtype == kBF16)
-    launch_kernel(matrix_memory_output_kernel<__nv_bfloat16>, tokens, threads, 0, s, (__nv_bfloat16*)out, o, proj, ld, g_off, weight, heads, dv, eps);
+    launch_kernel(matrix_memory_output_kernel<__nv_bfloat16>, grid, threads, 0, s, (__nv_bfloat16*)out, o, proj, ld, g_off, weight, heads, dv, eps);
   else
     return fail(1, "matrix_memory_output: unknown dtype %d", out_dtype);
   return check_launch("matrix_memory_output");

@@ -53,7 +53,7 @@ FAMILIES: dict[str, list[str]] = {
     "attention_latent_mma": ["attention_latent_mma.cu", "attention_mma.cuh", "common.cuh"],
     "head_prep": ["head_prep.cu", "common.cuh"],
     "matrix_memory": ["matrix_memory.cu", "common.cuh"],
-    "linear_heads": ["linear_heads.cu", "common.cuh"],
+    "linear_heads": ["linear_heads.cu", "attention_mma.cuh", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

@@ -128,7 +128,8 @@ def test_head_preparation_norm_rotation_and_page_write(dtype, layout, d, dims, r
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tokens, heads, n, k, tail", [(5, 3, 20, 8, 4), (70, 2, 33, 47, 0), (1, 6, 128, 32, 32), (40, 1, 8, 288, 16)])
+@pytest.mark.parametrize("tokens, heads, n, k, tail", [(5, 3, 20, 8, 4), (70, 2, 33, 47, 0), (1, 6, 128, 32, 32), (40, 1, 8, 288, 16),
+                                                        (130, 3, 100, 48, 8), (200, 2, 512, 128, 64)])
 def test_one_product_per_head_with_a_tail_passed_through(dtype, tokens, heads, n, k, tail):
     ops = _ops()
     x = torch.randn(tokens, heads, k + tail).to(dtype)
