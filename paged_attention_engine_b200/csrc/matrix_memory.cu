@@ -28,6 +28,12 @@ namespace {
 
 constexpr int TILE = 16;
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_group1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
 struct Scan {
   float* o;               // [tokens, heads, dv]
   float* state;           // [slots, heads, d * (dv + 1) + 1]
@@ -131,7 +137,7 @@ __global__ void matrix_memory_scan_kernel(const Scan p) {
 // registers, a warp owns 32 value columns and needs no other warp (every warp keeps a copy of n,
 // spread over its lanes, and sums n . q by shuffles), so a token costs no barrier: D fused
 // multiply-adds on the column, D more for its read-out (four partial sums), and q and k from
-// shared memory, 16 bytes at a time.
+// shared memory, 16 bytes at a time; q is used as projected and d^-1/2 multiplies the two sums.
 template <int D>
 __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const Scan p) {
   dependent_launch_prologue();
@@ -145,13 +151,28 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
   const int dv = p.dv, cols = p.cols;
   const int col = c0 + tid;
   const bool has_col = col < dv;
-  float* qs = smem;                                          // [TILE][D]
-  float* ks = qs + TILE * D;                                 // [TILE][D]
-  float* vs = ks + TILE * D;                                 // [TILE][cols]
-  float* gi = vs + TILE * cols;                              // [TILE]
-  float* gf = gi + TILE;                                     // [TILE]
+  // two stages of a tile: q [TILE][D], k [TILE][D], v [TILE][cols], log gates i [TILE], f [TILE]
+  const int stage_floats = TILE * (2 * D + cols) + 2 * TILE;
   const size_t per_head = (size_t)D * (dv + 1) + 1;
   float* st = p.state + ((size_t)p.state_slot[b] * p.heads + h) * per_head;
+  // A tile's q, k and v go to shared memory by asynchronous copies, one tile ahead: a block of
+  // one or a few warps cannot hide a trip to memory per element any other way.
+  auto issue = [&](int stage, int t0) {
+    float* qs = smem + stage * stage_floats;
+    float* ks = qs + TILE * D;
+    float* vs = ks + TILE * D;
+    const int n_tok = min(TILE, count - t0);
+    for (int e = tid; e < n_tok * D; e += cols) {
+      const int t = e / D, i = e - t * D;
+      const float* row = p.proj + (size_t)(first + t0 + t) * p.ld;
+      cp_async4(qs + e, row + p.q_off + h * D + i);
+      cp_async4(ks + e, row + p.k_off + h * D + i);
+    }
+    if (has_col)
+      for (int t = 0; t < n_tok; ++t) cp_async4(vs + t * cols + tid, p.proj + (size_t)(first + t0 + t) * p.ld + p.v_off + h * dv + col);
+  };
+  issue(0, 0);
+  cp_async_commit();
   float s[D];
 #pragma unroll
   for (int i = 0; i < D; ++i) s[i] = has_col ? st[(size_t)i * (dv + 1) + col] : 0.f;
@@ -160,17 +181,15 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
   for (int j = 0; j < NJ; ++j) n[j] = lane + 32 * j < D ? st[(size_t)(lane + 32 * j) * (dv + 1) + dv] : 0.f;
   float m = st[per_head - 1];
 
-  for (int t0 = 0; t0 < count; t0 += TILE) {
+  for (int t0 = 0, stage = 0; t0 < count; t0 += TILE, stage ^= 1) {
     const int n_tok = min(TILE, count - t0);
-    __syncthreads();                                         // the tile before is used up
-    for (int e = tid; e < n_tok * D; e += cols) {
-      const int t = e / D, i = e - t * D;
-      const float* row = p.proj + (size_t)(first + t0 + t) * p.ld;
-      qs[e] = row[p.q_off + h * D + i] * p.q_scale;
-      ks[e] = row[p.k_off + h * D + i];
-    }
-    for (int t = 0; t < n_tok; ++t)
-      vs[t * cols + tid] = has_col ? p.proj[(size_t)(first + t0 + t) * p.ld + p.v_off + h * dv + col] : 0.f;
+    float* qs = smem + stage * stage_floats;
+    float* ks = qs + TILE * D;
+    float* vs = ks + TILE * D;
+    float* gi = vs + TILE * cols;
+    float* gf = gi + TILE;
+    if (t0 + TILE < count) issue(stage ^ 1, t0 + TILE);      // that stage was used up before the barrier that ended the last round
+    cp_async_commit();
     if (tid < n_tok) {
       const float* row = p.proj + (size_t)(first + t0 + tid) * p.ld;
       const float a = row[p.i_off + h] + p.i_bias[h], g = row[p.f_off + h] + p.f_bias[h];
@@ -178,6 +197,7 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
       const float z = p.cap * tanhf(g / p.cap);
       gf[tid] = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));      // log sigmoid(z)
     }
+    cp_async_wait_group1();
     __syncthreads();
     for (int t = 0; t < n_tok; ++t) {
       const float li = gi[t], lf = gf[t];
@@ -195,9 +215,9 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
           part = fmaf(n[j], q[i], part);
         }
       }
-      part = warp_sum(part);
+      part = warp_sum(part) * p.q_scale;                      // n . (q / sqrt(d))
       const float below = fmaxf(fabsf(part), expf(-m)) + 1e-6f;
-      const float av = add * vs[t * cols + tid];
+      const float av = has_col ? add * vs[t * cols + tid] : 0.f;
       float num[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < D; i += 4) {
@@ -211,8 +231,10 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
         num[2] = fmaf(s[i + 2], q4.z, num[2]);
         num[3] = fmaf(s[i + 3], q4.w, num[3]);
       }
-      if (has_col) p.o[((size_t)(first + t0 + t) * p.heads + h) * dv + col] = ((num[0] + num[1]) + (num[2] + num[3])) / below;
+      if (has_col)
+        p.o[((size_t)(first + t0 + t) * p.heads + h) * dv + col] = ((num[0] + num[1]) + (num[2] + num[3])) * p.q_scale / below;
     }
+    __syncthreads();
   }
   if (has_col) {
 #pragma unroll
@@ -234,7 +256,13 @@ int launch_columns(Scan p, int seqs, int splits, cudaStream_t s) {
   int per_block = (warps + splits - 1) / splits;
   per_block = per_block > 4 ? 4 : per_block;
   p.cols = 32 * per_block;
-  const size_t smem = sizeof(float) * ((size_t)TILE * (2 * D + p.cols) + 2 * TILE);
+  const size_t smem = 2 * sizeof(float) * ((size_t)TILE * (2 * D + p.cols) + 2 * TILE);
+  static bool raised = false;
+  if (smem > 48 * 1024 && !raised) {
+    cudaError_t err = cudaFuncSetAttribute(matrix_memory_scan_columns_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (err != cudaSuccess) return fail(100, "matrix_memory: %s", cudaGetErrorString(err));
+    raised = true;
+  }
   launch_kernel(matrix_memory_scan_columns_kernel<D>, dim3((warps + per_block - 1) / per_block, p.heads, seqs), p.cols, smem, s, p);
   return check_launch("matrix_memory_scan");
 }

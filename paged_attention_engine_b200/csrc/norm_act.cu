@@ -83,6 +83,27 @@ __global__ void clamped_glu_kernel(TO* __restrict__ out, const TI* __restrict__ 
   out[i] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
 }
 
+// float32 rows whose half-width is a multiple of 4: four columns per thread, 16-byte loads.
+template <typename TO>
+__global__ void clamped_glu_f32x4_kernel(TO* __restrict__ out, const float* __restrict__ gate_up, long long quads, int inter,
+                                         float limit, float alpha) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= quads) return;
+  const int per_row = inter >> 2;
+  const long long t = i / per_row;
+  const int c = (int)(i - t * per_row) * 4;
+  const float4 g4 = *(const float4*)(gate_up + t * 2 * inter + c);
+  const float4 u4 = *(const float4*)(gate_up + t * 2 * inter + inter + c);
+  const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+  TO* to = out + t * inter + c;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float gate = fminf(g[e], limit), up = fminf(fmaxf(u[e], -limit), limit);
+    to[e] = from_float<TO>(gate / (1.f + expf(-alpha * gate)) * (up + 1.f));
+  }
+}
+
 // x <- cap * tanh(x / cap), float32 in place.
 __global__ void softcap_kernel(float* __restrict__ x, long long total, float cap) {
   dependent_launch_prologue();
@@ -285,6 +306,15 @@ PAE_EXPORT int pae_clamped_glu(void* out, const void* gate_up, int tokens, int i
   using bf = __nv_bfloat16;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   const int key = in_dtype * 10 + out_dtype;
+  if (in_dtype == kF32 && inter % 4 == 0 && ((uintptr_t)gate_up & 15) == 0 && (out_dtype == kF32 || out_dtype == kBF16)) {
+    const long long quads = total / 4;
+    const unsigned quad_blocks = (unsigned)((quads + 255) / 256);
+    if (out_dtype == kF32)
+      launch_kernel(clamped_glu_f32x4_kernel<float>, quad_blocks, 256, 0, s, (float*)out, (const float*)gate_up, quads, inter, limit, alpha);
+    else
+      launch_kernel(clamped_glu_f32x4_kernel<bf>, quad_blocks, 256, 0, s, (bf*)out, (const float*)gate_up, quads, inter, limit, alpha);
+    return check_launch("clamped_glu");
+  }
   if (key == 0)
     launch_kernel(clamped_glu_kernel<float, float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, total, inter, limit, alpha);
   else if (key == 1)
