@@ -5,11 +5,13 @@
 // (a latent of 512 and 64 rotated channels), so neither the queries nor the output fit one warp's
 // registers the way they do for head sizes up to 128:
 //
-//   * a block owns 16 query rows (16 consecutive tokens of one head, or, for a request that
-//     brings ONE token, 16 of its heads: every key is then read once for all of them) and walks
-//     the request's pages 64 keys at a time; the key tile is staged once by cp.async, two stages,
-//     rows padded by 16 bytes so that the eight rows of an ldmatrix fall into different banks;
-//   * scores: warp w computes the 16 x 16 block of the tile's keys 16w .. 16w+15 over all of D,
+//   * a block owns 32 query rows (32 consecutive tokens of one head, or, for a request that
+//     brings ONE token, 32 of its heads: every key is then read once for all of them) as two
+//     groups of four warps with 16 rows each, and walks the request's pages 64 keys at a time;
+//     the key tile is staged once for both groups by cp.async, two stages, rows padded by 16
+//     bytes so that the eight rows of an ldmatrix fall into different banks (a key tile of 576
+//     channels is 73 KB: one block an SM, so the second group is also what hides the first's latencies);
+//   * scores: warp w of a group computes the 16 x 16 block of the tile's keys 16w .. 16w+15 over all of D,
 //     its A fragments read from the query tile in shared memory, and leaves it as MMA fragments in
 //     shared memory; after a barrier every warp reads all four blocks and runs the same running
 //     softmax (the same instructions on the same numbers: the warps agree bit for bit);
@@ -26,7 +28,10 @@ using namespace pae_attention;
 
 namespace {
 
-constexpr int ROWS = 16;
+constexpr int GROUP_ROWS = 16;
+constexpr int GROUPS = 2;
+constexpr int ROWS = GROUP_ROWS * GROUPS;
+constexpr int THREADS = GROUPS * 128;
 constexpr int TILE = 64;
 constexpr int MAX_COLS = 128;            // value columns per warp
 
@@ -46,16 +51,16 @@ struct LatentParams {
   float* part_sum;
 };
 
-__global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
+__global__ void __launch_bounds__(THREADS) latent_kernel(const LatentParams p) {
   dependent_launch_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = threadIdx.x >> 7, warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;
   const int b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   const bool single = p.part_out != nullptr && q_count == 1;
   const int tile = single ? 0 : blockIdx.x, split = single ? blockIdx.x : 0;
-  const int head0 = single ? blockIdx.y * ROWS : blockIdx.y;          // single: a group of 16 heads
+  const int head0 = single ? blockIdx.y * ROWS : blockIdx.y;          // single: 32 of the token's heads
   if (single ? (split >= p.splits || head0 >= p.heads) : tile * ROWS >= q_count) return;
   const int rows = single ? min(ROWS, p.heads - head0) : min(ROWS, q_count - tile * ROWS);
   const int pos0 = p.q_pos0[b] + tile * ROWS;
@@ -65,11 +70,11 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
   const int row_bytes = D * 2 + 16;
   uint8_t* q_tile = smem;                                              // [ROWS][row_bytes]
   uint8_t* k_stage = q_tile + ROWS * row_bytes;                        // 2 x [TILE][row_bytes]
-  float* sbuf = (float*)(k_stage + 2 * TILE * row_bytes);              // [4][32][8]
+  float* sbuf = (float*)(k_stage + 2 * TILE * row_bytes) + group * 4 * 32 * 8;      // per group [4][32][8]
   const uint32_t q_u32 = smem_u32(q_tile), k_u32 = smem_u32(k_stage);
   const int* table = p.block_table + (size_t)b * p.table_width;
 
-  for (int i = threadIdx.x; i < ROWS * chunks; i += 128) {
+  for (int i = threadIdx.x; i < ROWS * chunks; i += THREADS) {
     const int r = i / chunks, c = i - r * chunks;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < rows) {
@@ -80,8 +85,8 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
     *(uint4*)(q_tile + r * row_bytes + c * 16) = v;
   }
 
-  // two threads per key row, each every other chunk; one page lookup per thread and tile
-  const int f_row = threadIdx.x >> 1, f_chunk0 = threadIdx.x & 1;
+  // four threads per key row, each every fourth chunk; one page lookup per thread and tile
+  const int f_row = threadIdx.x >> 2, f_chunk0 = threadIdx.x & 3;
   auto fetch = [&](int stage, int key0) {
     const int key = key0 + f_row;
     uint8_t* dst = k_stage + (size_t)stage * TILE * row_bytes + f_row * row_bytes;
@@ -90,9 +95,9 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
       const int page = checked_page(table[checked_table_index(index, p.table_width)]);
       const __nv_bfloat16* src = p.keys + ((size_t)page * p.page_size + (key - index * p.page_size)) * D;
       const uint32_t dst_u32 = smem_u32(dst);
-      for (int c = f_chunk0; c < chunks; c += 2) cp_async16(dst_u32 + c * 16, src + c * 8);
+      for (int c = f_chunk0; c < chunks; c += 4) cp_async16(dst_u32 + c * 16, src + c * 8);
     } else {
-      for (int c = f_chunk0; c < chunks; c += 2) *(uint4*)(dst + c * 16) = make_uint4(0, 0, 0, 0);
+      for (int c = f_chunk0; c < chunks; c += 4) *(uint4*)(dst + c * 16) = make_uint4(0, 0, 0, 0);
     }
   };
 
@@ -100,8 +105,10 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
 #pragma unroll
   for (int n = 0; n < MAX_COLS / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float row_max[2] = {-FLT_MAX, -FLT_MAX}, row_sum[2] = {0.f, 0.f};
-  const int my_pos[2] = {single ? pos0 : pos0 + (lane >> 2), single ? pos0 : pos0 + (lane >> 2) + 8};
-  const int last_pos = single ? pos0 : pos0 + rows - 1;
+  const int row0 = group * GROUP_ROWS;                                 // this group's first row of the block
+  const bool working = row0 < rows;                                    // a group without rows only helps to fetch
+  const int my_pos[2] = {single ? pos0 : pos0 + row0 + (lane >> 2), single ? pos0 : pos0 + row0 + (lane >> 2) + 8};
+  const int last_pos = single ? pos0 : pos0 + min(rows, row0 + GROUP_ROWS) - 1;
   const int c2 = (lane & 3) * 2;
   const int mid = lane >> 3, r8 = lane & 7;
   const float scale2 = p.scale * LOG2E;
@@ -122,25 +129,38 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
     cp_async_wait<1>();
     __syncthreads();
     const uint32_t k_tile = k_u32 + (t & 1) * TILE * row_bytes;
-    {                                    // scores of the keys 16 * warp .. + 15 of this tile
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const uint32_t a_at = q_u32 + (((lane >> 3) & 1) * 8 + r8) * row_bytes + (lane >> 4) * 16;
+    if (working) {                       // scores of the keys 16 * warp .. + 15 of this tile
+      // even and odd steps of D into accumulators of their own: two chains of dependent MMAs instead of one
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const uint32_t a_at = q_u32 + (row0 + ((lane >> 3) & 1) * 8 + r8) * row_bytes + (lane >> 4) * 16;
       const uint32_t b_at = k_tile + (warp * 16 + (mid >> 1) * 8 + r8) * row_bytes + (mid & 1) * 16;
-#pragma unroll 4
-      for (int k = 0; k < (D >> 4); ++k) {
-        uint32_t a[4], bb[4];
+      const int steps = D >> 4;
+#pragma unroll 2
+      for (int k = 0; k + 1 < steps; k += 2) {
+        uint32_t a[4], bb[4], a2[4], bb2[4];
         ldmatrix_x4(a, a_at + k * 32);
         ldmatrix_x4(bb, b_at + k * 32);
+        ldmatrix_x4(a2, a_at + k * 32 + 32);
+        ldmatrix_x4(bb2, b_at + k * 32 + 32);
+        mma_16816(s[0], a, bb[0], bb[1]);
+        mma_16816(s[1], a, bb[2], bb[3]);
+        mma_16816(s2[0], a2, bb2[0], bb2[1]);
+        mma_16816(s2[1], a2, bb2[2], bb2[3]);
+      }
+      if (steps & 1) {
+        uint32_t a[4], bb[4];
+        ldmatrix_x4(a, a_at + (steps - 1) * 32);
+        ldmatrix_x4(bb, b_at + (steps - 1) * 32);
         mma_16816(s[0], a, bb[0], bb[1]);
         mma_16816(s[1], a, bb[2], bb[3]);
       }
       float4* to = (float4*)(sbuf + ((size_t)warp * 32 + lane) * 8);
-      to[0] = make_float4(s[0][0], s[0][1], s[0][2], s[0][3]);
-      to[1] = make_float4(s[1][0], s[1][1], s[1][2], s[1][3]);
+      to[0] = make_float4(s[0][0] + s2[0][0], s[0][1] + s2[0][1], s[0][2] + s2[0][2], s[0][3] + s2[0][3]);
+      to[1] = make_float4(s[1][0] + s2[1][0], s[1][1] + s2[1][1], s[1][2] + s2[1][2], s[1][3] + s2[1][3]);
     }
     __syncthreads();
 #pragma unroll 1
-    for (int u = 0; u < TILE / 16; ++u) {
+    for (int u = 0; working && u < TILE / 16; ++u) {
       const int key0 = t * TILE + u * 16;
       if (key0 > last_pos || key0 >= kv_end) break;
       float s[2][4];
@@ -215,7 +235,7 @@ __global__ void __launch_bounds__(128) latent_kernel(const LatentParams p) {
 
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-    const int row = (lane >> 2) + half * 8;
+    const int row = row0 + (lane >> 2) + half * 8;
     if (row >= rows) continue;
     if (single) {
       const size_t at = ((size_t)b * p.heads + head0 + row) * p.splits + split;
@@ -277,7 +297,7 @@ __global__ void latent_merge_kernel(const LatentParams p) {
   }
 }
 
-size_t smem_bytes(int d) { return (size_t)(ROWS + 2 * TILE) * (d * 2 + 16) + 4 * 32 * 8 * sizeof(float); }
+size_t smem_bytes(int d) { return (size_t)(ROWS + 2 * TILE) * (d * 2 + 16) + GROUPS * 4 * 32 * 8 * sizeof(float); }
 
 }  // namespace
 
@@ -287,7 +307,7 @@ PAE_EXPORT int pae_attention_latent_mma_supports(int d, int dv) {
 }
 
 // bfloat16. out [tokens, heads, dv]; q [tokens, heads, d]; keys [pages, 1, page_size, d]. With `scratch`
-// (seqs * heads * splits * (dv + 2) floats) a request that brings ONE token is taken by blocks of up to 16
+// (seqs * heads * splits * (dv + 2) floats) a request that brings ONE token is taken by blocks of up to 32
 // heads each, its keys shared out over `splits` blocks and merged by a second kernel.
 PAE_EXPORT int pae_paged_attention_latent_mma(void* out, const void* q, const void* keys, const int* block_table,
                                               int table_width, const int* q_start, const int* q_pos0, const int* kv_len,
@@ -314,7 +334,7 @@ PAE_EXPORT int pae_paged_attention_latent_mma(void* out, const void* q, const vo
   cudaStream_t s = (cudaStream_t)stream;
   const int q_tiles = (max_q_len + ROWS - 1) / ROWS;
   dim3 grid(scratch != nullptr ? max(q_tiles, splits) : q_tiles, heads, seqs);
-  launch_kernel(latent_kernel, grid, 128, bytes, s, p);
+  launch_kernel(latent_kernel, grid, THREADS, bytes, s, p);
   if (int err = check_launch("paged_attention_latent_mma")) return err;
   if (scratch != nullptr) {
     const int threads = dv >= 512 ? 512 : (dv + 31) / 32 * 32;       // a column a thread

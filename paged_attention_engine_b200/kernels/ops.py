@@ -1148,14 +1148,14 @@ def paged_attention_scored(q, keys, values, block_table, q_start, q_pos0, kv_len
     if (in_keys and q.dtype == torch.bfloat16 and use_tensor_cores and form != "simt" and num_kv_heads == 1 and not window
             and not softcap and temp is None and r1 is None and sink is None):
         # Many heads over one latent key/value head (csrc/attention_latent_mma.cu). A request that brings one
-        # token is blocks of up to 16 heads; its keys are shared out (two tiles of 64 a block at least) until the launch fills the GPU once.
+        # token is blocks of up to 32 heads; its keys are shared out (two tiles of 64 a block at least) until the launch fills the GPU once.
         lib = _lib("attention_latent_mma")
         if lib.pae_attention_latent_mma_supports(head_dim, value_dim):
             _set_bounds("attention_latent_mma", keys)
             seqs = kv_len.numel()
             splits, scratch = 1, None
             if num_single is None or num_single > 0:
-                groups = -(-num_heads // 16)
+                groups = -(-num_heads // 32)
                 splits = max(1, min(-(-(max_kv_len or 0) // 128), _sm_count(q.device) // max(1, seqs * groups)))
                 scratch = torch.empty(seqs * num_heads * splits * (value_dim + 2), dtype=torch.float32, device=q.device)
             _check(lib, lib.pae_paged_attention_latent_mma(

@@ -243,11 +243,12 @@ def test_attention_whose_values_are_the_leading_channels_of_its_keys(dtype, c, r
 
 
 def test_latent_attention_on_tensor_cores_many_heads_long_contexts_and_batches():
-    """Sizes that the tensor-core kernel takes: more than 16 heads (two head groups for a single
-    token), contexts of many tiles shared out over blocks, single tokens beside portions."""
+    """Sizes that the tensor-core kernel takes: more heads than a block's 32 rows (two blocks for a
+    single token), fewer than one group of warps has, contexts of many tiles shared out over
+    blocks, single tokens beside portions."""
     ops = _ops()
     lib = ops._lib("attention_latent_mma")
-    for c, r, heads, page, T in ((64, 16, 20, 16, 300), (512, 64, 4, 16, 200), (128, 32, 6, 8, 530)):
+    for c, r, heads, page, T in ((64, 16, 40, 16, 300), (512, 64, 4, 16, 200), (128, 32, 20, 8, 530)):
         assert lib.pae_attention_latent_mma_supports(c + r, c) == 1
         rows, keys, table = _latent_rows(torch.bfloat16, T, c, r, page, -(-T // page) + 3, c + heads)
         q = (torch.randn(T, heads, c + r) * 0.5).to(torch.bfloat16)
