@@ -259,6 +259,105 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
 
 }  // namespace
 
+namespace {
+
+// For a float32 residual stream: value[row, :] = sum of splits + bias + residual (float32);
+// normed[row, :] = value / sqrt(mean(value^2) + eps) * weight in the engine's element type. The sum
+// of squares is double, as in the norm's own kernel.
+template <typename TO>
+__global__ void __launch_bounds__(512) splitk_rms_norm_cast_kernel(TO* __restrict__ normed, float* __restrict__ value,
+                                                                   const float* __restrict__ partial, int splits,
+                                                                   const float* __restrict__ bias, const float* __restrict__ residual,
+                                                                   const float* __restrict__ weight, int rows, int width, float eps) {
+  dependent_launch_prologue();
+  extern __shared__ float row_values[];       // [width]
+  __shared__ double reduce[32];
+  const int row = blockIdx.x;
+  const size_t plane = (size_t)rows * width;
+  double squares = 0.0;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const size_t at = (size_t)row * width + i;
+    float v = split_sum(partial, splits, plane, at);
+    if (bias != nullptr) v += bias[i];
+    if (residual != nullptr) v += residual[at];
+    value[at] = v;
+    row_values[i] = v;
+    squares = fma((double)v, (double)v, squares);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) reduce[warp] = squares;
+  __syncthreads();
+  double total = 0.0;
+  for (int i = 0; i < warps; ++i) total += reduce[i];       // every thread adds in the same order
+  const float scale = (float)(1.0 / sqrt(total / (double)width + (double)eps));
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    normed[(size_t)row * width + i] = from_float<TO>(row_values[i] * scale * weight[i]);
+}
+
+// out[t, c] = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), gate and
+// up the sums of the splits (+ bias) of columns c and inter + c.
+template <typename TO>
+__global__ void splitk_clamped_glu_kernel(TO* __restrict__ out, const float* __restrict__ partial, int splits,
+                                          const float* __restrict__ bias, int tokens, int inter, float limit, float alpha) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * inter) return;
+  const long long t = i / inter;
+  const int c = (int)(i - t * inter);
+  const size_t plane = (size_t)tokens * 2 * inter;
+  float g = split_sum(partial, splits, plane, (size_t)t * 2 * inter + c);
+  float u = split_sum(partial, splits, plane, (size_t)t * 2 * inter + inter + c);
+  if (bias != nullptr) {
+    g += bias[c];
+    u += bias[inter + c];
+  }
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  out[i] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+}  // namespace
+
+// value float32 [rows, width]; normed in out_dtype; partial float32 [splits, rows, width]; bias, residual (float32) may be null.
+PAE_EXPORT int pae_splitk_rms_norm_cast(void* normed, float* value, const float* partial, int splits, const float* bias,
+                                        const float* residual, const float* weight, int rows, int width, float eps,
+                                        int out_dtype, void* stream) {
+  if (rows == 0) return 0;
+  if ((size_t)width * sizeof(float) > 160 * 1024) return fail(2, "splitk_rms_norm_cast: rows of %d do not fit shared memory", width);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t bytes = (size_t)width * sizeof(float);
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 384 : (width >= 256 ? 128 : 64));
+  if (out_dtype == kBF16) {
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(splitk_rms_norm_cast_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    launch_kernel(splitk_rms_norm_cast_kernel<__nv_bfloat16>, rows, threads, bytes, s, (__nv_bfloat16*)normed, value, partial, splits,
+                  bias, residual, weight, rows, width, eps);
+  } else if (out_dtype == kF32) {
+    if (bytes > 48 * 1024) cudaFuncSetAttribute(splitk_rms_norm_cast_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    launch_kernel(splitk_rms_norm_cast_kernel<float>, rows, threads, bytes, s, (float*)normed, value, partial, splits, bias, residual,
+                  weight, rows, width, eps);
+  } else {
+    return fail(1, "splitk_rms_norm_cast: unknown dtype %d", out_dtype);
+  }
+  return check_launch("splitk_rms_norm_cast");
+}
+
+PAE_EXPORT int pae_splitk_clamped_glu(void* out, const float* partial, int splits, const float* bias, int tokens, int inter,
+                                      float limit, float alpha, int out_dtype, void* stream) {
+  const long long n = (long long)tokens * inter;
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == kBF16)
+    launch_kernel(splitk_clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, splits, bias, tokens, inter, limit, alpha);
+  else if (out_dtype == kF32)
+    launch_kernel(splitk_clamped_glu_kernel<float>, blocks, 256, 0, s, (float*)out, partial, splits, bias, tokens, inter, limit, alpha);
+  else
+    return fail(1, "splitk_clamped_glu: unknown dtype %d", out_dtype);
+  return check_launch("splitk_clamped_glu");
+}
+
 PAE_EXPORT int pae_splitk_rms_norm(void* normed, void* value, const float* partial, int splits, const float* bias,
                                    const void* residual, const float* weight, int rows, int width, float eps, int dtype,
                                    void* stream) {

@@ -882,9 +882,20 @@ def embedding_scaled(ids, table, scale: float, feedback=None) -> torch.Tensor:
 def rms_norm_cast(x, weight: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps) * weight over the last axis; x float32 or the engine's dtype, the
     result in `out_dtype` (x's when None)."""
+    _need(weight, "rms_norm_cast: weight", torch.float32)
+    if (isinstance(x, PendingSum) and x.value is None and not x.activation and x.dtype == torch.float32 and fuse_split_sums
+            and weight.numel() == x.shape[-1]):
+        # the sum of a split product (+ bias + residual) and the norm of the result as one kernel
+        splits, m, n = x.partial.shape
+        value = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        normed = torch.empty((m, n), dtype=out_dtype or torch.float32, device=x.device)
+        lib = _lib("fused_decode")
+        _check(lib, lib.pae_splitk_rms_norm_cast(_ptr(normed), _ptr(value), _ptr(x.partial), splits, _ptr(x.bias), _ptr(x.residual),
+                                                 _ptr(weight), m, n, eps, _code(normed), _stream()))
+        x.value = value
+        return normed
     x = materialized(x)
     _need(x, "rms_norm_cast: x")
-    _need(weight, "rms_norm_cast: weight", torch.float32)
     width = x.shape[-1]
     if weight.numel() != width:
         raise KernelError(f"rms_norm_cast: weight of {weight.numel()} for rows of {width}")
@@ -898,6 +909,14 @@ def rms_norm_cast(x, weight: torch.Tensor, eps: float, out_dtype=None) -> torch.
 def clamped_glu(gate_up, limit: float, alpha: float, out_dtype=None) -> torch.Tensor:
     """g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), for
     rows [tokens, 2 I] that hold the gate in columns [0, I) and the up projection in [I, 2 I)."""
+    if (isinstance(gate_up, PendingSum) and gate_up.value is None and gate_up.residual is None and not gate_up.activation
+            and fuse_split_sums and gate_up.shape[1] % 2 == 0 and out_dtype is not None):
+        splits, tokens, two_i = gate_up.partial.shape
+        out = torch.empty((tokens, two_i // 2), dtype=out_dtype, device=gate_up.device)
+        lib = _lib("fused_decode")
+        _check(lib, lib.pae_splitk_clamped_glu(_ptr(out), _ptr(gate_up.partial), splits, _ptr(gate_up.bias), tokens, two_i // 2,
+                                               float(limit), float(alpha), _code(out), _stream()))
+        return out
     gate_up = materialized(gate_up)
     _need(gate_up, "clamped_glu: gate_up")
     tokens, two_i = gate_up.shape

@@ -42,5 +42,6 @@ class MixerResidual(Block):
     roles = {"norm": "norm", "mixer": "mixer"}
 
     def forward(self, ctx, hidden, layer, cache):
-        hidden = ctx.ops.materialized(hidden)
-        return layer.mixer.forward(ctx, layer.norm.forward(ctx, hidden), hidden, cache)
+        # the norm may sum a product that is still in its splits; `materialized` then hands out that sum
+        normed = layer.norm.forward(ctx, hidden)
+        return layer.mixer.forward(ctx, normed, ctx.ops.materialized(hidden), cache)
