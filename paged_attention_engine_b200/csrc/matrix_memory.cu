@@ -13,7 +13,7 @@
 // (request, head, range of value columns); thread j keeps column j of S in shared memory (bank j:
 // no conflicts), and the last thread of every block keeps the column n, so n . q falls out of the
 // same loop as S^T q and every block can divide by itself (head sizes that are multiples of 16 up to
-// 128 take a second form of the kernel, further down, with the columns in registers). The tokens' q, k, v and gates come in
+// 128 take a second form of the kernel, further down, with the columns in registers of four threads). The tokens' q, k, v and gates come in
 // tiles of 16 tokens; the gates' transcendental functions are computed once per tile in parallel.
 // A token's arithmetic is the same instructions in the same order wherever a prompt was cut,
 // so the state is carried bit for bit across portions.
@@ -133,49 +133,63 @@ __global__ void matrix_memory_scan_kernel(const Scan p) {
   }
 }
 
-// The same recurrence for head sizes known at compile time: a thread keeps its column of S in
-// registers, a warp owns 32 value columns and needs no other warp (every warp keeps a copy of n,
-// spread over its lanes, and sums n . q by shuffles), so a token costs no barrier: D fused
-// multiply-adds on the column, D more for its read-out (four partial sums), and q and k from
-// shared memory, 16 bytes at a time; q is used as projected and d^-1/2 multiplies the two sums.
+// The same recurrence for head sizes known at compile time: a column of S lives in the registers
+// of KS = 4 threads, a quarter of its d key channels each (lanes 8 apart, so that neighbouring lanes
+// hold neighbouring columns and the state moves in full sectors); a warp owns 8 value columns and
+// needs no other warp (every warp keeps a copy of n, spread over its lanes, and sums n . q by
+// shuffles, as it sums a column's four partial read-outs), so a token costs no barrier. Four
+// times the warps of a thread-per-column form is what a single request's prompt needs: its
+// tokens come one after the other, and heads x dv / 8 warps are all the parallelism there is.
+// q is used as projected and d^-1/2 multiplies the two sums.
+constexpr int KS = 4;
+
 template <int D>
 __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const Scan p) {
   dependent_launch_prologue();
   extern __shared__ __align__(16) float smem[];
   constexpr int NJ = (D + 31) / 32;
+  constexpr int PER = D / KS;                                // key channels of a thread
+  constexpr int SEG = PER + 4;                               // a part's channels in shared memory, padded: the four parts' 16-byte loads meet no bank twice
+  constexpr int ROW = KS * SEG;                              // a token's q (or k) in shared memory
+  constexpr int WARP_COLS = 32 / KS;
   const int h = blockIdx.y, b = blockIdx.z;
-  const int c0 = blockIdx.x * p.cols;                        // p.cols: a multiple of 32, the block's threads
+  const int c0 = blockIdx.x * p.cols;                        // p.cols = 8 x the block's warps
   const int first = p.q_start[b], count = p.q_start[b + 1] - first;
   if (c0 >= p.dv || count <= 0) return;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, threads = blockDim.x;
   const int dv = p.dv, cols = p.cols;
-  const int col = c0 + tid;
+  const int part = lane / WARP_COLS;                         // which quarter of the key channels
+  const int local = warp * WARP_COLS + lane % WARP_COLS;     // the column within the block
+  const int col = c0 + local;
   const bool has_col = col < dv;
-  // two stages of a tile: q [TILE][D], k [TILE][D], v [TILE][cols], log gates i [TILE], f [TILE]
-  const int stage_floats = TILE * (2 * D + cols) + 2 * TILE;
+  auto at = [](int i) { return (i / PER) * SEG + i % PER; };  // where key channel i of a token lies in shared memory
+  // two stages of a tile: q [TILE][ROW], k [TILE][ROW], v [TILE][cols], log gates i [TILE], f [TILE]
+  const int stage_floats = TILE * (2 * ROW + cols) + 2 * TILE;
   const size_t per_head = (size_t)D * (dv + 1) + 1;
   float* st = p.state + ((size_t)p.state_slot[b] * p.heads + h) * per_head;
   // A tile's q, k and v go to shared memory by asynchronous copies, one tile ahead: a block of
-  // one or a few warps cannot hide a trip to memory per element any other way.
+  // a few warps cannot hide a trip to memory per element any other way.
   auto issue = [&](int stage, int t0) {
     float* qs = smem + stage * stage_floats;
-    float* ks = qs + TILE * D;
-    float* vs = ks + TILE * D;
+    float* ks = qs + TILE * ROW;
+    float* vs = ks + TILE * ROW;
     const int n_tok = min(TILE, count - t0);
-    for (int e = tid; e < n_tok * D; e += cols) {
+    for (int e = tid; e < n_tok * D; e += threads) {
       const int t = e / D, i = e - t * D;
       const float* row = p.proj + (size_t)(first + t0 + t) * p.ld;
-      cp_async4(qs + e, row + p.q_off + h * D + i);
-      cp_async4(ks + e, row + p.k_off + h * D + i);
+      cp_async4(qs + t * ROW + at(i), row + p.q_off + h * D + i);
+      cp_async4(ks + t * ROW + at(i), row + p.k_off + h * D + i);
     }
-    if (has_col)
-      for (int t = 0; t < n_tok; ++t) cp_async4(vs + t * cols + tid, p.proj + (size_t)(first + t0 + t) * p.ld + p.v_off + h * dv + col);
+    for (int e = tid; e < n_tok * cols; e += threads) {
+      const int t = e / cols, j = e - t * cols;
+      if (c0 + j < dv) cp_async4(vs + e, p.proj + (size_t)(first + t0 + t) * p.ld + p.v_off + h * dv + c0 + j);
+    }
   };
   issue(0, 0);
   cp_async_commit();
-  float s[D];
+  float s[PER];
 #pragma unroll
-  for (int i = 0; i < D; ++i) s[i] = has_col ? st[(size_t)i * (dv + 1) + col] : 0.f;
+  for (int i = 0; i < PER; ++i) s[i] = has_col ? st[(size_t)(part * PER + i) * (dv + 1) + col] : 0.f;
   float n[NJ];
 #pragma unroll
   for (int j = 0; j < NJ; ++j) n[j] = lane + 32 * j < D ? st[(size_t)(lane + 32 * j) * (dv + 1) + dv] : 0.f;
@@ -184,8 +198,8 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
   for (int t0 = 0, stage = 0; t0 < count; t0 += TILE, stage ^= 1) {
     const int n_tok = min(TILE, count - t0);
     float* qs = smem + stage * stage_floats;
-    float* ks = qs + TILE * D;
-    float* vs = ks + TILE * D;
+    float* ks = qs + TILE * ROW;
+    float* vs = ks + TILE * ROW;
     float* gi = vs + TILE * cols;
     float* gf = gi + TILE;
     if (t0 + TILE < count) issue(stage ^ 1, t0 + TILE);      // that stage was used up before the barrier that ended the last round
@@ -204,24 +218,26 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
       const float m_new = fmaxf(lf + m, li);
       const float keep = expf(lf + m - m_new), add = expf(li - m_new);
       m = m_new;
-      const float* q = qs + t * D;
-      const float* k = ks + t * D;
-      float part = 0.f;
+      const float* q = qs + t * ROW;
+      const float* k = ks + t * ROW;
+      float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
         const int i = lane + 32 * j;
         if (i < D) {
-          n[j] = fmaf(keep, n[j], add * k[i]);
-          part = fmaf(n[j], q[i], part);
+          n[j] = fmaf(keep, n[j], add * k[at(i)]);
+          dot = fmaf(n[j], q[at(i)], dot);
         }
       }
-      part = warp_sum(part) * p.q_scale;                      // n . (q / sqrt(d))
-      const float below = fmaxf(fabsf(part), expf(-m)) + 1e-6f;
-      const float av = has_col ? add * vs[t * cols + tid] : 0.f;
+      dot = warp_sum(dot) * p.q_scale;                        // n . (q / sqrt(d))
+      const float below = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+      const float av = has_col ? add * vs[t * cols + local] : 0.f;
+      const float* kp = k + part * SEG;
+      const float* qp = q + part * SEG;
       float num[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < D; i += 4) {
-        const float4 k4 = *(const float4*)(k + i), q4 = *(const float4*)(q + i);
+      for (int i = 0; i < PER; i += 4) {
+        const float4 k4 = *(const float4*)(kp + i), q4 = *(const float4*)(qp + i);
         s[i] = fmaf(keep, s[i], k4.x * av);
         s[i + 1] = fmaf(keep, s[i + 1], k4.y * av);
         s[i + 2] = fmaf(keep, s[i + 2], k4.z * av);
@@ -231,14 +247,16 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
         num[2] = fmaf(s[i + 2], q4.z, num[2]);
         num[3] = fmaf(s[i + 3], q4.w, num[3]);
       }
-      if (has_col)
-        p.o[((size_t)(first + t0 + t) * p.heads + h) * dv + col] = ((num[0] + num[1]) + (num[2] + num[3])) * p.q_scale / below;
+      float total = (num[0] + num[1]) + (num[2] + num[3]);
+      total += __shfl_xor_sync(0xffffffffu, total, WARP_COLS);          // the column's other quarters
+      total += __shfl_xor_sync(0xffffffffu, total, 2 * WARP_COLS);
+      if (has_col && part == 0) p.o[((size_t)(first + t0 + t) * p.heads + h) * dv + col] = total * p.q_scale / below;
     }
     __syncthreads();
   }
   if (has_col) {
 #pragma unroll
-    for (int i = 0; i < D; ++i) st[(size_t)i * (dv + 1) + col] = s[i];
+    for (int i = 0; i < PER; ++i) st[(size_t)(part * PER + i) * (dv + 1) + col] = s[i];
   }
   // every block of a head read n and m of the state when it started: see the kernel above
   if (blockIdx.x == 0 && warp == 0) {
@@ -252,18 +270,19 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_columns_kernel(const S
 
 template <int D>
 int launch_columns(Scan p, int seqs, int splits, cudaStream_t s) {
-  const int warps = (p.dv + 31) / 32;
+  constexpr int WARP_COLS = 32 / KS, ROW = KS * (D / KS + 4);
+  const int warps = (p.dv + WARP_COLS - 1) / WARP_COLS;
   int per_block = (warps + splits - 1) / splits;
   per_block = per_block > 4 ? 4 : per_block;
-  p.cols = 32 * per_block;
-  const size_t smem = 2 * sizeof(float) * ((size_t)TILE * (2 * D + p.cols) + 2 * TILE);
+  p.cols = WARP_COLS * per_block;
+  const size_t smem = 2 * sizeof(float) * ((size_t)TILE * (2 * ROW + p.cols) + 2 * TILE);
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
     cudaError_t err = cudaFuncSetAttribute(matrix_memory_scan_columns_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (err != cudaSuccess) return fail(100, "matrix_memory: %s", cudaGetErrorString(err));
     raised = true;
   }
-  launch_kernel(matrix_memory_scan_columns_kernel<D>, dim3((warps + per_block - 1) / per_block, p.heads, seqs), p.cols, smem, s, p);
+  launch_kernel(matrix_memory_scan_columns_kernel<D>, dim3((warps + per_block - 1) / per_block, p.heads, seqs), 32 * per_block, smem, s, p);
   return check_launch("matrix_memory_scan");
 }
 
