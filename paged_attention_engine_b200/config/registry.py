@@ -212,14 +212,16 @@ def zugarax_spec(cfg: ZugaraxConfig) -> ModelSpec:
         m = layer.mixer
         cache_from = None
         if layer.type == "attention":
-            scaling = dict(m.rot.scaling, kind="banded") if m.rot.scaling is not None else None
+            encoding = None
+            if m.rot is not None:
+                scaling = dict(m.rot.scaling, kind="banded") if m.rot.scaling is not None else None
+                encoding = {"kind": "scaled_rotary", "dims": m.rot.dims, "base": m.rot.base, "scaling": scaling}
             mixer = PartSpec(
                 "gated_window_attention",
                 {
                     "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
                     "value_dim": m.vdim, "scale": m.scale, "window": m.window, "qk_norm_eps": cfg.norm_eps,
-                    "unit_sink": True, "output_gate": True,
-                    "position_encoding": {"kind": "scaled_rotary", "dims": m.rot.dims, "base": m.rot.base, "scaling": scaling},
+                    "unit_sink": True, "output_gate": True, "position_encoding": encoding,
                 },
                 f"{prefix}.mix",
             )

@@ -7,7 +7,7 @@ A layer's mixer is one of three kinds:
 
   attention         heads, kv_heads, dim (query/key head size), vdim, scale, mask {size} (absent:
                     every earlier key), rot {base, dims, scaling {factor, low, high, original}}
-                    (`scaling` absent: plain frequencies).
+                    (`scaling` absent: plain frequencies; `rot` absent: no rotation).
   latent_attention  heads, dim (unrotated query/key channels per head), rot_dim (rotated ones),
                     vdim, kv_rank (the latent's size), scale, rot {base, dims, scaling {factor,
                     original, fast, slow}}, kv_from (absent: the layer projects its own latent; j:
@@ -82,11 +82,12 @@ class WindowAttention:
     vdim: int
     scale: float
     window: int             # 0: every earlier key
-    rot: Rotation
+    rot: Rotation | None    # None: positions are not encoded
 
     def to_dict(self) -> dict[str, Any]:
-        out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-               "rot": self.rot.to_dict()}
+        out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.rot is not None:
+            out["rot"] = self.rot.to_dict()
         if self.window:
             out["mask"] = {"size": self.window}
         return out
@@ -167,12 +168,12 @@ class ZugaraxConfig:
                 window = 0
                 if mixer_raw.get("mask") is not None:
                     window = _positive(_get(mixer_raw["mask"], "size", int, m + "mask."), m + "mask.size")
-                rot = Rotation.read(mixer_raw.get("rot"), m + "rot.", ("factor", "low", "high", "original"))
+                rot = None
+                if mixer_raw.get("rot") is not None:
+                    rot = Rotation.read(mixer_raw.get("rot"), m + "rot.", ("factor", "low", "high", "original"))
                 dim = size("dim")
-                if rot.dims > dim:
+                if rot is not None and rot.dims > dim:
                     raise ConfigError(f"config.json: {m}rot.dims {rot.dims} exceeds dim {dim}")
-                if rot.scaling is not None and dict(rot.scaling)["high"] == dict(rot.scaling)["low"]:
-                    raise ConfigError(f"config.json: {m}rot.scaling.high equals low")
                 mixer: Any = WindowAttention(heads, kv_heads, dim, size("vdim"), _get(mixer_raw, "scale", float, m), window, rot)
             elif kind == "latent_attention":
                 rot = Rotation.read(mixer_raw.get("rot"), m + "rot.", ("factor", "original", "fast", "slow"))

@@ -48,7 +48,8 @@ def banded_frequencies(freqs, factor: float, low: float, high: float, original: 
         elif wavelength > original / low:
             out.append(f / factor)
         else:
-            s = (original / wavelength - low) / (high - low)
+            # high == low leaves no band between the two: a wavelength on the one border is kept
+            s = (original / wavelength - low) / (high - low) if high != low else 1.0
             out.append((1.0 - s) * f / factor + s * f)
     return out
 

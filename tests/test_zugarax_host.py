@@ -33,6 +33,11 @@ def test_absent_keys_mean_absent_mechanisms():
     assert cfg.layers[0].mixer.window == 12 and dict(cfg.layers[0].mixer.rot.scaling)["low"] == 0.5
     assert cfg.layers[2].ff == 0 and cfg.layers[4].mixer.kv_from == 1
     assert ZugaraxConfig.from_dict(zh.SMALL_C).logit_softcap == 0.0
+    bare = json.loads(json.dumps(zh.ONLY_ATTENTION))
+    bare["layers"][0]["mixer"].pop("rot")
+    cfg_bare, spec_bare = resolve(bare)
+    assert cfg_bare.layers[0].mixer.rot is None and spec_bare.layers[0].mixer.params["position_encoding"] is None
+    assert cfg_bare.to_dict() == bare
     names = collect_tensor_specs(resolve(zh.SMALL_A)[1])
     assert "l4.mix.dkv" not in names and "l4.mix.dkv.norm" not in names and "l1.mix.dkv" in names
     assert "l2.norm2" not in names and "l2.mlp.gate" not in names
