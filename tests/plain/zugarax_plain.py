@@ -27,10 +27,6 @@ def rms_norm(x, weight, eps):
     return y if weight is None else y * _f(weight)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 # --------------------------------------------------------------------------- #
 # Rotation frequencies
 # --------------------------------------------------------------------------- #
@@ -114,12 +110,13 @@ def windowed_attention_mixer(h, tensors, prefix, m, eps, rows=None):
     q = rms_norm((h @ t("q").T).view(T, H, d), tensors[f"{prefix}.q.norm"], eps)
     k = rms_norm((h @ t("k").T).view(T, G, d), tensors[f"{prefix}.k.norm"], eps)
     v = (h @ t("v").T).view(T, G, dv)
-    rot = m["rot"]
-    sc = rot.get("scaling")
-    freqs = (banded_frequencies(rot["dims"], rot["base"], sc["factor"], sc["low"], sc["high"], sc["original"])
-             if sc else base_frequencies(rot["dims"], rot["base"]))
-    positions = list(range(T))
-    q, k = rotate(q, positions, freqs, "half"), rotate(k, positions, freqs, "half")
+    rot = m.get("rot")
+    if rot is not None:
+        sc = rot.get("scaling")
+        freqs = (banded_frequencies(rot["dims"], rot["base"], sc["factor"], sc["low"], sc["high"], sc["original"])
+                 if sc else base_frequencies(rot["dims"], rot["base"]))
+        positions = list(range(T))
+        q, k = rotate(q, positions, freqs, "half"), rotate(k, positions, freqs, "half")
     size = m["mask"]["size"] if m.get("mask") else None
     o = softmax_attention(q, k, v, m["scale"], size=size, extra_one=True, rows=rows)
     gate = torch.sigmoid(h @ t("g").T)

@@ -76,9 +76,12 @@ SMALL_C = config(97, 48, [
 ], 6.9)
 ONLY_MEMORY = config(97, 48, [memory(2, 24, 24, 4.0, ff=64), memory(3, 16, 40, 15.0)], 3.0, softcap=4.0)
 ONLY_ATTENTION = config(97, 48, [attention(4, 2, 12, 20, 0.3, 6, size=10, scaling=(4.0, 1.0, 4.0, 16), ff=64, limit=0.8)], 7.0)
+# Neither a rotation nor a window: attention that knows no positions but the causal order.
+BARE_ATTENTION = config(97, 48, [attention(2, 1, 24, 24, 0.2, 8, ff=64), memory(2, 8, 12, 5.0)], 5.0)
+del BARE_ATTENTION["layers"][0]["mixer"]["rot"]
 ONLY_LATENT = config(97, 48, [latent(4, 12, 8, 20, 24, 0.3, scaling=(4.0, 16, 8.0, 1.0), ff=64)], 7.0)
 SMALL = {"small_b": (SMALL_B, 16, 21), "small_a": (SMALL_A, 4, 22), "small_c": (SMALL_C, 8, 23), "only_memory": (ONLY_MEMORY, 8, 24),
-         "only_attention": (ONLY_ATTENTION, 4, 25), "only_latent": (ONLY_LATENT, 16, 26)}       # config, page size, seed
+         "only_attention": (ONLY_ATTENTION, 4, 25), "only_latent": (ONLY_LATENT, 16, 26), "bare_attention": (BARE_ATTENTION, 16, 27)}       # config, page size, seed
 
 
 def write_model(folder: Path, raw: dict, seed: int, dtype=torch.bfloat16, sharpen: float = 6.0) -> Path:
